@@ -1,0 +1,136 @@
+/*
+ * C ABI of the B200 (sm_100a) FlashAttention-2 library, libfa2_b200.so.
+ *
+ * Plain pointers and sizes only: device pointers are raw CUDA addresses, `stream` is a
+ * cudaStream_t / CUstream passed as void*. Every call enqueues work on `stream` and returns
+ * without synchronising. Return value: 0 on success, a negative FA2_E_* code on failure;
+ * fa2_last_error() returns the message of the last failure on the calling thread.
+ *
+ * These entry points are what the host layer of the reference crate (flash-attn2-rs, Rust)
+ * would bind through `extern "C"` in place of its own cuLaunchKernel calls; the tvm-ffi
+ * operator symbols (__tvm_ffi_fwd, ...) in libflash_attn2_b200.so sit on top of them.
+ * All tensors use the reference layouts: Q/O [B, Sq, H, D], K/V [B, Sk, Hk, D] (last stride 1),
+ * LSE fp32 [B, H, Sq]; packed (varlen) Q/O [total_q, H, D], K/V [total_k, Hk, D],
+ * LSE fp32 [H, total_q].
+ */
+#ifndef FA2_B200_H_
+#define FA2_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define FA2_API __attribute__((visibility("default")))
+#else
+#define FA2_API
+#endif
+
+#define FA2_F16 0
+#define FA2_BF16 1
+
+#define FA2_OK 0
+#define FA2_E_VALUE (-1)   /* bad shape / stride / argument value */
+#define FA2_E_TYPE (-2)    /* bad dtype */
+#define FA2_E_RUNTIME (-3) /* CUDA failure, or a kernel reported a stalled pipeline */
+
+/* Strides are in elements: {batch, row, head}; the head_dim stride is 1. In packed mode
+ * the batch stride is ignored. */
+typedef struct fa2_fwd_args {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;                   /* [B, Sq, H, D] (or packed), same dtype as q */
+  float* lse;                  /* contiguous fp32 [B, H, Sq] (or [H, total_q]) */
+  const float* alibi_slopes;   /* fp32 [H] or [B, H], or NULL */
+  int32_t alibi_batch_stride;  /* 0 for [H], H for [B, H] */
+  int32_t dtype;               /* FA2_F16 or FA2_BF16 */
+  int32_t batch, seqlen_q, seqlen_k, heads, heads_k, head_dim;
+  int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3];
+  float softmax_scale;
+  int32_t causal;
+  int32_t window_left, window_right; /* < 0 = unbounded, as passed by the caller */
+  float softcap;                     /* 0 = off */
+  /* packed (varlen) mode when cu_seqlens_q != NULL: device int32 [batch + 1] each;
+   * seqlen_q / seqlen_k are then the maxima and total_q / total_k the packed row counts */
+  const int32_t* cu_seqlens_q;
+  const int32_t* cu_seqlens_k;
+  int32_t total_q, total_k;
+} fa2_fwd_args;
+
+/* Dense forward. Replaces launch_forward + flash_attn_fwd of the reference
+ * (flash-attn2-rs/src/host/forward/mod.rs:449-813, src/device/forward/dense.rs:472-590).
+ * Empty Sk gives O = 0 and LSE = +inf (forward/mod.rs:548-582). */
+FA2_API int fa2_fwd(const fa2_fwd_args* args, void* stream);
+
+/* Packed variable-length forward driven by cu_seqlens on the device, no host read of the
+ * metadata. Replaces varlen_fwd (flash-attn2-rs/src/host/varlen/mod.rs:21-630,
+ * src/device/varlen/mod.rs:30-318,445-578). */
+FA2_API int fa2_varlen_fwd(const fa2_fwd_args* args, void* stream);
+
+/* delta[b,h,s] = sum_d dO*O in fp32, rows padded to a multiple of 128 and the padding zeroed:
+ * delta is [B, H, ceil(Sq/128)*128]. Replaces bwd_preprocess
+ * (flash-attn2-rs/src/host/backward.rs:628-737, src/device/backward/reduce.rs:40-108). */
+typedef struct fa2_bwd_preprocess_args {
+  const void* dout;
+  const void* out;
+  float* delta;
+  int32_t dtype;
+  int32_t batch, seqlen_q, heads, head_dim;
+  int64_t do_stride[3], o_stride[3];
+  /* packed mode (varlen_preprocess, src/device/varlen/backward.rs:53-132):
+   * delta is [H, total_q + 128*batch], sequence b starts at cu_seqlens_q[b] + 128*b */
+  const int32_t* cu_seqlens_q;
+  int32_t total_q;
+} fa2_bwd_preprocess_args;
+FA2_API int fa2_bwd_preprocess(const fa2_bwd_preprocess_args* args, void* stream);
+
+/* Backward: dQ, dK, dV from Q, K, V, dO, LSE and delta. dQ is accumulated in fp32 in
+ * `dq_accum` (fa2_bwd_workspace_bytes() bytes, 16-byte aligned, need not be cleared) and
+ * converted to the 16-bit dQ at the end. `which` selects outputs: bit 0 = dQ, bit 1 = dK and dV.
+ * Replaces backward_component + the `backward` and `backward_kv` kernels
+ * (flash-attn2-rs/src/host/backward.rs:14-566, src/device/backward/dq.rs:12-302,438-576,
+ *  src/device/backward/dkv.rs:15-266,865-1012). */
+typedef struct fa2_bwd_args {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* dout;
+  const float* lse;    /* [B, H, Sq] (or [H, total_q]) */
+  const float* delta;  /* layout of fa2_bwd_preprocess */
+  void* dq;            /* [B, Sq, H, D] contiguous, input dtype */
+  void* dk;            /* [B, Sk, Hk, D] contiguous */
+  void* dv;
+  void* dq_accum;      /* fp32 workspace */
+  int64_t dq_accum_bytes;
+  int32_t dtype;
+  int32_t batch, seqlen_q, seqlen_k, heads, heads_k, head_dim;
+  int64_t q_stride[3], k_stride[3], v_stride[3], do_stride[3];
+  float softmax_scale;
+  int32_t causal;
+  int32_t window_left, window_right;
+  int32_t which;
+  const int32_t* cu_seqlens_q;
+  const int32_t* cu_seqlens_k;
+  int32_t total_q, total_k;
+} fa2_bwd_args;
+FA2_API int64_t fa2_bwd_workspace_bytes(const fa2_bwd_args* args);
+FA2_API int fa2_bwd(const fa2_bwd_args* args, void* stream);
+
+/* Message of the last failed call on this thread ("" if none). */
+FA2_API const char* fa2_last_error(void);
+
+/* Synchronises `device` and returns the kernels' status word: 0 = every pipeline wait
+ * completed; otherwise the code of the first wait that ran out (the kernels bound every
+ * wait instead of spinning forever). Clears the word. Negative on CUDA failure. */
+FA2_API int fa2_device_status(int device);
+
+/* Number of SMs the persistent kernels size their grids for on `device`. */
+FA2_API int fa2_sm_count(int device);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA2_B200_H_ */

@@ -1,0 +1,46 @@
+// Kernel-side parameter blocks shared by the host launchers and the sm_100a kernels.
+#pragma once
+#include <cuda.h>
+#include <stdint.h>
+
+namespace fa2 {
+
+// Error codes a kernel leaves in its status word when a bounded wait runs out.
+enum WaitSite : int {
+  kWaitNone = 0,
+  kWaitLoadQEmpty = 11,
+  kWaitLoadKVEmpty = 12,
+  kWaitMmaQFull = 21,
+  kWaitMmaKVFull = 22,
+  kWaitMmaPFull = 23,
+  kWaitMmaOFree = 24,
+  kWaitSoftmaxSFull = 31,
+  kWaitSoftmaxPvDone = 32,
+  kWaitEpiFinal = 41,
+  kWaitEpiPvDone = 42,
+  kWaitBwd = 50,
+};
+
+struct FwdParams {
+  CUtensorMap tm_q, tm_k, tm_v, tm_o;  // 4-D maps: (D, heads, rows, batch), box (64, 1, 128, 1)
+  void* o_ptr;                         // for the predicated (non-TMA) output path
+  float* lse_ptr;
+  const int32_t* cu_q;                 // packed (varlen) mode when non-null
+  const int32_t* cu_k;
+  const float* alibi;                  // [H] or [B,H] slopes, or null
+  int64_t o_row_stride, o_head_stride, o_batch_stride;  // elements
+  int64_t lse_head_stride, lse_batch_stride;            // elements
+  int alibi_batch_stride;
+  int batch, heads, heads_k, seqlen_q, seqlen_k;        // seqlen_* = maxima in packed mode
+  int group;                           // heads / heads_k
+  int num_mblk;                        // ceil(seqlen_q / 256)
+  int num_tiles;                       // num_mblk * batch * heads
+  int window_left, window_right;       // normalised; < 0 = open side
+  int causal_alibi;                    // causal ALiBi depends on the key position only
+  float scale;                         // softmax scale (applied before softcap / mask)
+  float scale_log2;                    // scale * log2(e)
+  float softcap;                       // 0 = off
+  int* status;                         // device status word (0 = ok)
+};
+
+}  // namespace fa2
