@@ -1,0 +1,123 @@
+// HBM-bound helpers of the backward pass:
+//   * delta = rowsum(dO * O) in fp32, written into the padded layouts the reference uses
+//     (flash-attn2-rs/src/device/backward/reduce.rs:40-108, src/device/varlen/backward.rs:53-132);
+//   * the final dQ = 16-bit(scale * fp32 accumulator) conversion
+//     (same shape as the reference's backward_dq_merge, reduce.rs:164-197).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include "fa2_params.h"
+#include "fa2_launch.h"
+
+namespace fa2 {
+
+namespace {
+
+template <bool BF16>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+  if constexpr (BF16) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  } else {
+    const __half2 h = *reinterpret_cast<const __half2*>(&w);
+    return __half22float2(h);
+  }
+}
+
+// One group of LANES threads per (batch, row, head); each thread reads 16 bytes at a time.
+// Rows are enumerated over the padded length so the padding is written as zero.
+template <bool BF16, int LANES>
+__global__ void __launch_bounds__(256) preprocess_kernel(const PreprocessParams p) {
+  const int64_t gid = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) / LANES;
+  const int lane = threadIdx.x % LANES;
+  const int64_t total = static_cast<int64_t>(p.batch) * p.seqlen_pad * p.heads;
+  if (gid >= total) return;
+  const int h = static_cast<int>(gid % p.heads);
+  const int64_t bs = gid / p.heads;
+  const int s = static_cast<int>(bs % p.seqlen_pad);
+  const int b = static_cast<int>(bs / p.seqlen_pad);
+  int64_t row = s;     // row inside the input tensors
+  int64_t drow = s;    // row inside delta
+  bool live = s < p.seqlen_q;
+  int bq = b;
+  if (p.cu_q != nullptr) {
+    const int q0 = p.cu_q[b];
+    const int len = p.cu_q[b + 1] - q0;
+    live = s < len;
+    row = q0 + s;
+    drow = q0 + 128 * b + s;
+    bq = 0;
+    // Padding of a packed sequence: only the 128-row tail that belongs to it.
+    if (s >= (len + 127) / 128 * 128) return;
+  }
+  float sum = 0.f;
+  if (live) {
+    const uint4* a = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.dout) + bq * p.do_batch_stride +
+                                                    row * p.do_row_stride + h * p.do_head_stride);
+    const uint4* o = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.out) + bq * p.o_batch_stride +
+                                                    row * p.o_row_stride + h * p.o_head_stride);
+    for (int i = lane; i < p.head_dim / 8; i += LANES) {
+      const uint4 x = a[i], y = o[i];
+      const uint32_t xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 fx = unpack2<BF16>(xs[k]), fy = unpack2<BF16>(ys[k]);
+        sum = fmaf(fx.x, fy.x, sum);
+        sum = fmaf(fx.y, fy.y, sum);
+      }
+    }
+  }
+#pragma unroll
+  for (int d = LANES / 2; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d, LANES);
+  if (lane == 0) p.delta[bq * p.delta_batch_stride + h * p.delta_head_stride + drow] = sum;
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(256) dq_convert_kernel(const float4* __restrict__ src, uint4* __restrict__ dst,
+                                                         int64_t n8, float scale) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float4 a = src[2 * i], b = src[2 * i + 1];
+    uint4 w;
+    if constexpr (BF16) {
+      __nv_bfloat162 t0 = __floats2bfloat162_rn(a.x * scale, a.y * scale), t1 = __floats2bfloat162_rn(a.z * scale, a.w * scale);
+      __nv_bfloat162 t2 = __floats2bfloat162_rn(b.x * scale, b.y * scale), t3 = __floats2bfloat162_rn(b.z * scale, b.w * scale);
+      w = make_uint4(*reinterpret_cast<uint32_t*>(&t0), *reinterpret_cast<uint32_t*>(&t1),
+                     *reinterpret_cast<uint32_t*>(&t2), *reinterpret_cast<uint32_t*>(&t3));
+    } else {
+      __half2 t0 = __floats2half2_rn(a.x * scale, a.y * scale), t1 = __floats2half2_rn(a.z * scale, a.w * scale);
+      __half2 t2 = __floats2half2_rn(b.x * scale, b.y * scale), t3 = __floats2half2_rn(b.z * scale, b.w * scale);
+      w = make_uint4(*reinterpret_cast<uint32_t*>(&t0), *reinterpret_cast<uint32_t*>(&t1),
+                     *reinterpret_cast<uint32_t*>(&t2), *reinterpret_cast<uint32_t*>(&t3));
+    }
+    dst[i] = w;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_bwd_preprocess(const PreprocessParams& p, cudaStream_t stream) {
+  const int64_t groups = static_cast<int64_t>(p.batch) * p.seqlen_pad * p.heads;
+  if (groups == 0) return cudaSuccess;
+  const int lanes = p.head_dim <= 64 ? 8 : 16;
+  const int64_t threads = groups * lanes;
+  const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
+  if (p.bf16) {
+    if (lanes == 8) preprocess_kernel<true, 8><<<grid, 256, 0, stream>>>(p);
+    else preprocess_kernel<true, 16><<<grid, 256, 0, stream>>>(p);
+  } else {
+    if (lanes == 8) preprocess_kernel<false, 8><<<grid, 256, 0, stream>>>(p);
+    else preprocess_kernel<false, 16><<<grid, 256, 0, stream>>>(p);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dq_convert(const float* src, void* dst, int64_t n, float scale, bool bf16, cudaStream_t stream) {
+  const int64_t n8 = n / 8;
+  if (n8 == 0) return cudaSuccess;
+  const int64_t want = (n8 + 255) / 256;
+  const unsigned grid = static_cast<unsigned>(want < 148 * 16 ? want : 148 * 16);
+  if (bf16) dq_convert_kernel<true><<<grid, 256, 0, stream>>>(reinterpret_cast<const float4*>(src), reinterpret_cast<uint4*>(dst), n8, scale);
+  else dq_convert_kernel<false><<<grid, 256, 0, stream>>>(reinterpret_cast<const float4*>(src), reinterpret_cast<uint4*>(dst), n8, scale);
+  return cudaGetLastError();
+}
+
+}  // namespace fa2

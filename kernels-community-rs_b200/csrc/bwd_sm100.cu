@@ -1,0 +1,533 @@
+// FlashAttention-2 backward for sm_100a (B200): dQ, dK, dV in one kernel.
+//
+// One CTA owns 128 keys of one (batch, kv head) and walks every 128-row query block (and every
+// query head of the GQA group) that can see those keys. Everything is computed transposed, keys
+// on the TMEM lanes, so that P^T feeds the dV MMA straight from TMEM:
+//
+//   S^T  = K Q^T            smem x smem  -> TMEM [keys x q]
+//   dP^T = V dO^T           smem x smem  -> TMEM [keys x q]
+//   P^T  = exp2(S^T c - lse)             compute warps, written back over S^T as 16-bit
+//   dV  += P^T dO           TMEM x smem (dO as MN-major operand)
+//   dS^T = P^T (dP^T - delta)            compute warps -> swizzled smem [keys x q]
+//   dK  += dS^T Q           smem (K-major view of dS^T) x smem (Q MN-major)
+//   dQ   = dS K             smem (MN-major view of dS^T) x smem (K MN-major) -> TMEM, aliasing dP^T
+//   dQ tile -> registers -> smem -> cp.reduce.async.bulk (fp32 add) into the dQ accumulator
+//
+// TMEM: dK [0,D) dV [D,2D) S^T/P^T [256,384) dP^T/dQ [384,512).
+// Warps: 0 loader (TMA), 1 MMA issuer, 4-11 compute (two warpgroups, 64 query columns each),
+// 12-15 dQ drain. dK and dV are accumulated over the whole loop in TMEM and written once, so they
+// need no atomics; the GQA heads are walked serially like the reference kernel does.
+//
+// Replaces the reference kernels `backward` (dQ) and `backward_kv`
+// (flash-attn2-rs/src/device/backward/dq.rs:12-302,438-576, dkv.rs:15-266,865-1012,
+//  common.rs:121-152) and their packed variants (src/device/varlen/backward.rs:134-648), with
+// fp32 dQ accumulation in global memory as in the reference's fused kernel (common.rs:248-252).
+#include "sm100_ptx.cuh"
+#include "fa2_params.h"
+#include "fa2_launch.h"
+
+namespace fa2 {
+
+namespace {
+
+constexpr int kBlk = 128;  // keys per CTA and query rows per iteration
+constexpr int kThreads = 512;
+constexpr int kComputeRegs = 176;
+constexpr int kDrainRegs = 104;
+constexpr int kMiscRegs = 56;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int D>
+struct BwdCfg {
+  static constexpr int kAtoms = D / 64;
+  static constexpr int kTileBytes = kBlk * D * 2;
+  static constexpr int kKOff = 0;
+  static constexpr int kVOff = kTileBytes;
+  static constexpr int kQOff = 2 * kTileBytes;     // 2 stages
+  static constexpr int kDOOff = 4 * kTileBytes;    // 1 stage
+  static constexpr int kDSOff = 5 * kTileBytes;    // [128 keys x 128 q] 16-bit
+  static constexpr int kDSBytes = kBlk * kBlk * 2;
+  static constexpr int kStageOff = kDSOff + kDSBytes;  // dQ staging: [128 rows x 32 fp32]
+  static constexpr int kStageBytes = kBlk * 128;
+  static constexpr int kBarOff = kStageOff + kStageBytes;
+  static constexpr int kNumBars = 20;
+  static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+  static constexpr int kStatOff = kMiscOff + 32;       // lse / delta: [2 buffers][2][128] fp32
+  static constexpr int kSmemBytes = kStatOff + 2 * 2 * kBlk * 4 + 1024;
+  static constexpr uint32_t kTmemDK = 0, kTmemDV = D, kTmemS = 256, kTmemDP = 384;
+};
+
+struct KvTile {
+  int b, hk, n0;
+  int sq, sk, q_row0, k_row0, bq, off;
+  int m_start, n_m, n_iter;
+  bool valid;
+};
+
+__device__ __forceinline__ KvTile get_kv_tile(const BwdParams& p, int t) {
+  KvTile ti;
+  const int bh = p.batch * p.heads_k;
+  const int nblk = t / bh;
+  const int rem = t - nblk * bh;
+  ti.b = rem / p.heads_k;
+  ti.hk = rem - ti.b * p.heads_k;
+  ti.n0 = nblk * kBlk;
+  if (p.cu_q != nullptr) {
+    ti.q_row0 = p.cu_q[ti.b];
+    ti.sq = p.cu_q[ti.b + 1] - ti.q_row0;
+    ti.k_row0 = p.cu_k[ti.b];
+    ti.sk = p.cu_k[ti.b + 1] - ti.k_row0;
+    ti.bq = 0;
+    if (ti.sq < 0 || ti.sk < 0 || ti.sq > p.seqlen_q || ti.sk > p.seqlen_k) ti.sk = 0;
+  } else {
+    ti.q_row0 = 0;
+    ti.k_row0 = 0;
+    ti.sq = p.seqlen_q;
+    ti.sk = p.seqlen_k;
+    ti.bq = ti.b;
+  }
+  ti.off = ti.sk - ti.sq;
+  ti.valid = ti.n0 < ti.sk;
+  // Query rows that can see a key of [n0, n0 + 127].
+  int q_lo = 0, q_hi = ti.sq;  // [q_lo, q_hi)
+  const int n_last = min(ti.n0 + kBlk - 1, ti.sk - 1);
+  if (p.window_right >= 0) q_lo = max(0, ti.n0 - ti.off - p.window_right);
+  if (p.window_left >= 0) q_hi = min(ti.sq, n_last - ti.off + p.window_left + 1);
+  ti.m_start = q_lo / kBlk;
+  ti.n_m = (q_hi > q_lo) ? ((q_hi + kBlk - 1) / kBlk - ti.m_start) : 0;
+  ti.n_iter = ti.n_m * p.group;
+  return ti;
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant__ BwdParams p) {
+  using Cfg = BwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* s_k = smem + Cfg::kKOff;
+  uint8_t* s_v = smem + Cfg::kVOff;
+  uint8_t* s_q = smem + Cfg::kQOff;
+  uint8_t* s_do = smem + Cfg::kDOOff;
+  uint8_t* s_ds = smem + Cfg::kDSOff;
+  uint8_t* s_stage = smem + Cfg::kStageOff;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOff);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* q_full = bars + 1;   // [2]
+  uint64_t* q_empty = bars + 3;  // [2]
+  uint64_t* do_full = bars + 5;
+  uint64_t* do_empty = bars + 6;
+  uint64_t* s_full = bars + 7;
+  uint64_t* p_full = bars + 8;
+  uint64_t* dp_full = bars + 9;
+  uint64_t* ds_full = bars + 10;
+  uint64_t* dq_full = bars + 11;
+  uint64_t* dq_free = bars + 12;
+  uint64_t* dkv_done = bars + 13;
+  uint64_t* stat_full = bars + 14;
+  uint64_t* stage_free = bars + 15;
+  uint64_t* stage_full = bars + 16;
+  uint64_t* epi_full = bars + 17;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kMiscOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::kMiscOff + 8);
+  float* s_stat = reinterpret_cast<float*>(smem + Cfg::kStatOff);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const WaitCtl ctl{abort_flag, p.status};
+  const KvTile ti = get_kv_tile(p, blockIdx.x);
+  if (!ti.valid) return;
+  const bool want_dq = (p.which & 1) != 0;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+    }
+    mbar_init(do_full, 1);
+    mbar_init(do_empty, 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 256);
+    mbar_init(dp_full, 1);
+    mbar_init(ds_full, 256);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_free, 128);
+    mbar_init(dkv_done, 1);
+    mbar_init(stat_full, 256);
+    mbar_init(stage_free, 1);
+    mbar_init(stage_full, kBlk);
+    mbar_init(&epi_full[0], kBlk);
+    mbar_init(&epi_full[1], kBlk);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&p.tm_q);
+    tma_prefetch_desc(&p.tm_k);
+    tma_prefetch_desc(&p.tm_v);
+    tma_prefetch_desc(&p.tm_do);
+    tma_prefetch_desc(&p.tm_dqa);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const int n_iter = ti.n_iter;
+
+  if (warp < 4) {
+    reg_dealloc<kMiscRegs>();
+    if (warp == 0 && lane == 0) {
+      // ---------------------------------------------------------------- loader
+      if (n_iter > 0) mbar_expect_tx(kv_full, 2 * Cfg::kTileBytes);
+#pragma unroll
+      for (int a = 0; a < Cfg::kAtoms && n_iter > 0; ++a) {
+        tma_load_4d(s_k + a * (kBlk * 128), &p.tm_k, kv_full, a * 64, ti.hk, ti.k_row0 + ti.n0, ti.bq);
+        tma_load_4d(s_v + a * (kBlk * 128), &p.tm_v, kv_full, a * 64, ti.hk, ti.k_row0 + ti.n0, ti.bq);
+      }
+      bool ok = true;
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int hq = ti.hk * p.group + it / ti.n_m;
+        const int m0 = (ti.m_start + it % ti.n_m) * kBlk;
+        const int st = it & 1;
+        ok = mbar_wait(&q_empty[st], ((it >> 1) & 1) ^ 1, ctl, kWaitBwd + 1);
+        if (!ok) break;
+        mbar_expect_tx(&q_full[st], Cfg::kTileBytes);
+#pragma unroll
+        for (int a = 0; a < Cfg::kAtoms; ++a)
+          tma_load_4d(s_q + st * Cfg::kTileBytes + a * (kBlk * 128), &p.tm_q, &q_full[st], a * 64, hq,
+                      ti.q_row0 + m0, ti.bq);
+        ok = mbar_wait(do_empty, (it & 1) ^ 1, ctl, kWaitBwd + 2);
+        if (!ok) break;
+        mbar_expect_tx(do_full, Cfg::kTileBytes);
+#pragma unroll
+        for (int a = 0; a < Cfg::kAtoms; ++a)
+          tma_load_4d(s_do + a * (kBlk * 128), &p.tm_do, do_full, a * 64, hq, ti.q_row0 + m0, ti.bq);
+      }
+      if (!ok) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {
+        }
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ---------------------------------------------------------------- mma issuer
+      const uint32_t idesc_qk = make_idesc(BF16, kBlk, kBlk, false, false);  // S^T, dP^T
+      const uint32_t idesc_dv = make_idesc(BF16, kBlk, D, false, true);      // dV (A in TMEM), dK
+      const uint32_t idesc_dq = make_idesc(BF16, kBlk, D, true, true);       // dQ
+      const uint32_t k_addr = smem_u32(s_k), v_addr = smem_u32(s_v), q_addr = smem_u32(s_q);
+      const uint32_t do_addr = smem_u32(s_do), ds_addr = smem_u32(s_ds);
+      auto kmajor_pair = [&](uint32_t d_tmem, uint32_t a_base, uint32_t b_base) {
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t o = (ks / 4) * (kBlk * 128) + (ks % 4) * 32;
+          mma_ss(d_tmem, make_smem_desc(a_base + o, 16, 1024), make_smem_desc(b_base + o, 16, 1024), idesc_qk, ks > 0);
+        }
+      };
+      bool ok = n_iter > 0;
+      if (ok) ok = mbar_wait(kv_full, 0, ctl, kWaitBwd + 3);
+      if (ok) ok = mbar_wait(&q_full[0], 0, ctl, kWaitBwd + 4);
+      if (ok) {
+        tc_fence_after();
+        kmajor_pair(tmem + Cfg::kTmemS, k_addr, q_addr);
+        mma_commit(s_full);
+        ok = mbar_wait(do_full, 0, ctl, kWaitBwd + 5);
+      }
+      if (ok) {
+        tc_fence_after();
+        kmajor_pair(tmem + Cfg::kTmemDP, v_addr, do_addr);
+        mma_commit(dp_full);
+      }
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int st = it & 1;
+        const uint32_t q_it = q_addr + st * Cfg::kTileBytes;
+        const bool has_next = it + 1 < n_iter;
+        // dV += P^T dO   (P^T: two 32-column halves at S + 0 and S + 64)
+        ok = mbar_wait(p_full, it & 1, ctl, kWaitBwd + 6);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < kBlk / 16; ++ks) {
+          const uint32_t a_tmem = tmem + Cfg::kTmemS + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8);
+          mma_ts(tmem + Cfg::kTmemDV, a_tmem, make_smem_desc(do_addr + ks * 2048, kBlk * 128, 1024), idesc_dv,
+                 it > 0 || ks > 0);
+        }
+        mma_commit(do_empty);
+        // dQ = dS K   (into the dP^T columns, which the compute warps have drained)
+        ok = mbar_wait(ds_full, it & 1, ctl, kWaitBwd + 7);
+        if (!ok) break;
+        tc_fence_after();
+        if (want_dq) {
+#pragma unroll
+          for (int ks = 0; ks < kBlk / 16; ++ks)
+            mma_ss(tmem + Cfg::kTmemDP, make_smem_desc(ds_addr + ks * 2048, kBlk * 128, 1024),
+                   make_smem_desc(k_addr + ks * 2048, kBlk * 128, 1024), idesc_dq, ks > 0);
+          mma_commit(dq_full);
+        }
+        // S^T of the next iteration
+        if (has_next) {
+          ok = mbar_wait(&q_full[st ^ 1], ((it + 1) >> 1) & 1, ctl, kWaitBwd + 8);
+          if (!ok) break;
+          tc_fence_after();
+          kmajor_pair(tmem + Cfg::kTmemS, k_addr, q_addr + (st ^ 1) * Cfg::kTileBytes);
+          mma_commit(s_full);
+        }
+        // dK += dS^T Q
+#pragma unroll
+        for (int ks = 0; ks < kBlk / 16; ++ks) {
+          const uint32_t o = (ks / 4) * (kBlk * 128) + (ks % 4) * 32;
+          mma_ss(tmem + Cfg::kTmemDK, make_smem_desc(ds_addr + o, 16, 1024),
+                 make_smem_desc(q_it + ks * 2048, kBlk * 128, 1024), idesc_dv, it > 0 || ks > 0);
+        }
+        mma_commit(&q_empty[st]);
+        // dP^T of the next iteration, once the dQ tile has left TMEM
+        if (has_next) {
+          ok = mbar_wait(do_full, (it + 1) & 1, ctl, kWaitBwd + 9);
+          if (ok && want_dq) ok = mbar_wait(dq_free, it & 1, ctl, kWaitBwd + 10);
+          if (!ok) break;
+          tc_fence_after();
+          kmajor_pair(tmem + Cfg::kTmemDP, v_addr, do_addr);
+          mma_commit(dp_full);
+        }
+      }
+      if (ok) mma_commit(dkv_done);
+    }
+  } else if (warp < 12) {
+    // ------------------------------------------------------------------ compute
+    reg_alloc<kComputeRegs>();
+    const int cw = warp - 4;
+    const int wg = cw >> 2;                 // which 64 query columns
+    const int key_in = (cw & 3) * 32 + lane;
+    const int ct = tid - 128;               // 0..255
+    const uint32_t lane_addr = static_cast<uint32_t>((cw & 3) * 32) << 16;
+    const uint32_t t_s = tmem + lane_addr + Cfg::kTmemS + wg * 64;
+    const uint32_t t_dp = tmem + lane_addr + Cfg::kTmemDP + wg * 64;
+    const int kpos = ti.n0 + key_in;
+    bool ok = true;
+    for (int it = 0; it < n_iter; ++it) {
+      const int hq = ti.hk * p.group + it / ti.n_m;
+      const int m0 = (ti.m_start + it % ti.n_m) * kBlk;
+      float* stat = s_stat + (it & 1) * (2 * kBlk);
+      {
+        // Stage this block's LSE (log2 domain) and delta; rows past the sequence give P = 0.
+        const int r = ct & 127;
+        const int q = m0 + r;
+        float val;
+        if (ct < kBlk) {
+          val = INFINITY;
+          if (q < ti.sq) val = p.lse[ti.bq * p.lse_batch_stride + hq * p.lse_head_stride + ti.q_row0 + q] * kLog2e;
+        } else {
+          val = 0.f;
+          if (q < ti.sq)
+            val = p.delta[ti.bq * p.delta_batch_stride + hq * p.delta_head_stride + ti.q_row0 + ti.b * p.delta_seq_pad + q];
+        }
+        stat[ct] = val;
+      }
+      mbar_arrive(stat_full);
+      if (!mbar_wait(stat_full, it & 1, ctl, kWaitBwd + 15)) { ok = false; break; }
+      const float4* lse4 = reinterpret_cast<const float4*>(stat + wg * 64);
+      const float4* dl4 = reinterpret_cast<const float4*>(stat + kBlk + wg * 64);
+
+      // ---- phase A: P^T = exp2(S^T c - lse)
+      if (!mbar_wait(s_full, it & 1, ctl, kWaitBwd + 11)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sr[64];
+      tmem_ld32(t_s, sr);
+      tmem_ld32(t_s + 32, sr + 32);
+      tmem_wait_ld();
+      const int qbase = m0 + wg * 64;
+      bool need_mask = (ti.n0 + kBlk > ti.sk);
+      if (p.window_right >= 0) need_mask |= (ti.n0 + kBlk - 1 > m0 + ti.off + p.window_right);
+      if (p.window_left >= 0) need_mask |= (ti.n0 < m0 + kBlk - 1 + ti.off - p.window_left);
+      int c_lo = 0, c_hi = 64;
+      if (need_mask) {
+        if (p.window_right >= 0) c_lo = kpos - ti.off - p.window_right - qbase;
+        if (p.window_left >= 0) c_hi = kpos - ti.off + p.window_left + 1 - qbase;
+        if (kpos >= ti.sk) c_hi = -1;
+      }
+      float pr[64];
+#pragma unroll
+      for (int i = 0; i < 64; i += 4) {
+        const float4 l4 = lse4[i / 4];
+        pr[i] = ex2(fmaf(__uint_as_float(sr[i]), p.scale_log2, -l4.x));
+        pr[i + 1] = ex2(fmaf(__uint_as_float(sr[i + 1]), p.scale_log2, -l4.y));
+        pr[i + 2] = ex2(fmaf(__uint_as_float(sr[i + 2]), p.scale_log2, -l4.z));
+        pr[i + 3] = ex2(fmaf(__uint_as_float(sr[i + 3]), p.scale_log2, -l4.w));
+      }
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (i < c_lo || i >= c_hi) pr[i] = 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) sr[i] = pack2<BF16>(pr[2 * i], pr[2 * i + 1]);
+      tmem_st32(t_s, sr);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(p_full);
+
+      // ---- phase B: dS^T = P^T (dP^T - delta)
+      if (!mbar_wait(dp_full, it & 1, ctl, kWaitBwd + 12)) { ok = false; break; }
+      tc_fence_after();
+      tmem_ld32(t_dp, sr);
+      tmem_ld32(t_dp + 32, sr + 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      uint8_t* ds_row = s_ds + wg * (kBlk * 128) + key_in * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float4 d0 = dl4[2 * c], d1 = dl4[2 * c + 1];
+        const int i = c * 8;
+        uint4 w;
+        w.x = pack2<BF16>(pr[i] * (__uint_as_float(sr[i]) - d0.x), pr[i + 1] * (__uint_as_float(sr[i + 1]) - d0.y));
+        w.y = pack2<BF16>(pr[i + 2] * (__uint_as_float(sr[i + 2]) - d0.z), pr[i + 3] * (__uint_as_float(sr[i + 3]) - d0.w));
+        w.z = pack2<BF16>(pr[i + 4] * (__uint_as_float(sr[i + 4]) - d1.x), pr[i + 5] * (__uint_as_float(sr[i + 5]) - d1.y));
+        w.w = pack2<BF16>(pr[i + 6] * (__uint_as_float(sr[i + 6]) - d1.z), pr[i + 7] * (__uint_as_float(sr[i + 7]) - d1.w));
+        *reinterpret_cast<uint4*>(ds_row + ((c ^ (key_in & 7)) << 4)) = w;
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(ds_full);
+    }
+    // ---- epilogue: warpgroup 0 writes dK (scaled), warpgroup 1 writes dV
+    if (ok) {
+      const uint32_t t_acc = tmem + lane_addr + (wg == 0 ? Cfg::kTmemDK : Cfg::kTmemDV);
+      const float mul = (wg == 0) ? p.scale : 1.f;
+      const CUtensorMap* tm = (wg == 0) ? &p.tm_dk : &p.tm_dv;
+      uint16_t* gptr = reinterpret_cast<uint16_t*>(wg == 0 ? p.dk_ptr : p.dv_ptr);
+      const bool store = (p.which & 2) != 0;
+      const bool tma_store = (p.cu_k == nullptr) || (ti.n0 + kBlk <= ti.sk);
+      uint8_t* stage = s_q + wg * Cfg::kTileBytes;
+      bool done = true;
+      if (n_iter > 0) done = mbar_wait(dkv_done, 0, ctl, kWaitBwd + 13);
+      if (done && store) {
+        tc_fence_after();
+        uint16_t* grow = gptr + ti.bq * p.dkv_batch_stride + static_cast<int64_t>(ti.k_row0 + kpos) * p.dkv_row_stride +
+                         ti.hk * p.dkv_head_stride;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t acc[32];
+          if (n_iter > 0) {
+            tmem_ld32(t_acc + c * 32, acc);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] = 0;
+          }
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            w[i] = pack2<BF16>(__uint_as_float(acc[2 * i]) * mul, __uint_as_float(acc[2 * i + 1]) * mul);
+          if (tma_store) {
+            uint8_t* rowp = stage + (c / 2) * (kBlk * 128) + key_in * 128;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              *reinterpret_cast<uint4*>(rowp + ((((c & 1) * 4 + q) ^ (key_in & 7)) << 4)) =
+                  make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+          } else if (kpos < ti.sk) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              *reinterpret_cast<uint4*>(grow + c * 32 + q * 8) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+          }
+        }
+        if (tma_store) {
+          fence_proxy_async_smem();
+          mbar_arrive(&epi_full[wg]);
+          if ((ct & 127) == 0 && mbar_wait(&epi_full[wg], 0, ctl, kWaitBwd + 16)) {
+#pragma unroll
+            for (int a = 0; a < Cfg::kAtoms; ++a)
+              tma_store_4d(tm, stage + a * (kBlk * 128), a * 64, ti.hk, ti.k_row0 + ti.n0, ti.bq);
+            tma_commit_group();
+            tma_wait_group<0>();
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ dQ drain
+    reg_dealloc<kDrainRegs>();
+    const int rt = tid - 384;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t t_dq = tmem + lane_addr + Cfg::kTmemDP;
+    uint8_t* rowp = s_stage + rt * 128;
+    if (want_dq) {
+      uint32_t n_piece = 0;
+      bool ok = true;
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int hq = ti.hk * p.group + it / ti.n_m;
+        const int m0 = (ti.m_start + it % ti.n_m) * kBlk;
+        if (!mbar_wait(dq_full, it & 1, ctl, kWaitBwd + 14)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int half = 0; half < D / 64; ++half) {
+          uint32_t acc[64];
+          tmem_ld32(t_dq + half * 64, acc);
+          tmem_ld32(t_dq + half * 64 + 32, acc + 32);
+          tmem_wait_ld();
+          if (half == D / 64 - 1) {
+            tc_fence_before();
+            mbar_arrive(dq_free);
+          }
+#pragma unroll
+          for (int piece = 0; piece < 2; ++piece) {
+            // The previous reduce must have finished reading the staging buffer.
+            if (rt == 0) {
+              tma_wait_group_read<0>();
+              mbar_arrive(stage_free);
+            }
+            if (!mbar_wait(stage_free, n_piece & 1, ctl, kWaitBwd + 17)) { ok = false; break; }
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+              *reinterpret_cast<uint4*>(rowp + ((c ^ (rt & 7)) << 4)) =
+                  make_uint4(acc[piece * 32 + 4 * c], acc[piece * 32 + 4 * c + 1], acc[piece * 32 + 4 * c + 2],
+                             acc[piece * 32 + 4 * c + 3]);
+            fence_proxy_async_smem();
+            mbar_arrive(stage_full);
+            if (rt == 0) {
+              if (!mbar_wait(stage_full, n_piece & 1, ctl, kWaitBwd + 18)) { ok = false; break; }
+              tma_reduce_add_4d(&p.tm_dqa, s_stage, half * 64 + piece * 32, hq, ti.q_row0 + m0, ti.bq);
+              tma_commit_group();
+            }
+            ++n_piece;
+          }
+          if (!ok) break;
+        }
+      }
+      if (rt == 0) tma_wait_group<0>();
+    }
+  }
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+template <int D, bool BF16>
+cudaError_t launch_one(const BwdParams& p, int num_ctas, cudaStream_t stream) {
+  using Cfg = BwdCfg<D>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e =
+        cudaFuncSetAttribute(bwd_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  bwd_kernel<D, BF16><<<num_ctas, kThreads, Cfg::kSmemBytes, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_bwd(const BwdParams& p, int head_dim, bool bf16, cudaStream_t stream) {
+  const int num_ctas = p.num_nblk * p.batch * p.heads_k;
+  if (num_ctas <= 0) return cudaSuccess;
+  if (head_dim == 128) return bf16 ? launch_one<128, true>(p, num_ctas, stream) : launch_one<128, false>(p, num_ctas, stream);
+  if (head_dim == 64) return bf16 ? launch_one<64, true>(p, num_ctas, stream) : launch_one<64, false>(p, num_ctas, stream);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace fa2

@@ -254,9 +254,191 @@ int fwd_common(const fa2_fwd_args* a, void* stream_v, bool packed) {
   return FA2_OK;
 }
 
+int bwd_preprocess_impl(const fa2_bwd_preprocess_args* a, void* stream_v) {
+  if (a == nullptr) return fail(FA2_E_VALUE, "args is null");
+  if (a->dtype != FA2_F16 && a->dtype != FA2_BF16) return fail(FA2_E_TYPE, "dout and out must be float16 or bfloat16");
+  const int d = a->head_dim;
+  const bool packed = a->cu_seqlens_q != nullptr;
+  if (a->batch <= 0 || a->heads <= 0 || a->batch > 65535 || a->heads > 65535 || a->seqlen_q < 0 || d < 8 || d > 256 ||
+      d % 8 != 0)
+    return fail(FA2_E_VALUE, "unsupported backward tensor dimensions");
+  if (a->seqlen_q == 0 || (packed && a->total_q == 0)) return FA2_OK;
+  if (a->dout == nullptr || a->out == nullptr || a->delta == nullptr)
+    return fail(FA2_E_VALUE, "dout, out and delta must be non-null");
+  const int ns = packed ? 2 : 3;
+  int rc;
+  if ((rc = check_layout(a->dout, a->do_stride + (packed ? 1 : 0), ns, "dout")) != FA2_OK) return rc;
+  if ((rc = check_layout(a->out, a->o_stride + (packed ? 1 : 0), ns, "out")) != FA2_OK) return rc;
+  fa2::PreprocessParams p;
+  memset(&p, 0, sizeof(p));
+  p.dout = a->dout;
+  p.out = a->out;
+  p.delta = a->delta;
+  p.cu_q = a->cu_seqlens_q;
+  p.do_batch_stride = packed ? 0 : a->do_stride[0];
+  p.do_row_stride = a->do_stride[1];
+  p.do_head_stride = a->do_stride[2];
+  p.o_batch_stride = packed ? 0 : a->o_stride[0];
+  p.o_row_stride = a->o_stride[1];
+  p.o_head_stride = a->o_stride[2];
+  p.batch = a->batch;
+  p.heads = a->heads;
+  p.seqlen_q = a->seqlen_q;
+  p.seqlen_pad = (a->seqlen_q + 127) / 128 * 128;
+  p.head_dim = d;
+  p.bf16 = a->dtype == FA2_BF16;
+  if (packed) {
+    p.delta_head_stride = static_cast<int64_t>(a->total_q) + 128LL * a->batch;
+    p.delta_batch_stride = 0;
+  } else {
+    p.delta_head_stride = p.seqlen_pad;
+    p.delta_batch_stride = static_cast<int64_t>(a->heads) * p.seqlen_pad;
+  }
+  cudaError_t e = fa2::launch_bwd_preprocess(p, static_cast<cudaStream_t>(stream_v));
+  if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "preprocess launch failed: %s", cudaGetErrorString(e));
+  return FA2_OK;
+}
+
+int64_t bwd_rows(const fa2_bwd_args* a) {
+  return a->cu_seqlens_q != nullptr ? static_cast<int64_t>(a->total_q)
+                                    : static_cast<int64_t>(a->batch) * a->seqlen_q;
+}
+
+int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
+  if (a == nullptr) return fail(FA2_E_VALUE, "args is null");
+  if (a->dtype != FA2_F16 && a->dtype != FA2_BF16) return fail(FA2_E_TYPE, "q, k, v must be float16 or bfloat16");
+  const bool packed = a->cu_seqlens_q != nullptr;
+  const int d = a->head_dim;
+  if (d > 256 || d < 8 || d % 8 != 0) return fail(FA2_E_VALUE, "unsupported backward tensor dimensions");
+  if (d != 64 && d != 128) return fail(FA2_E_VALUE, "head dim %d is not built for sm_100a yet (64 and 128 are)", d);
+  if (a->heads_k <= 0 || a->heads % a->heads_k != 0)
+    return fail(FA2_E_VALUE, "num_heads (%d) must be a multiple of num_heads_k (%d)", a->heads, a->heads_k);
+  if (a->batch <= 0 || a->heads <= 0 || a->batch > 65535 || a->heads > 65535 || a->seqlen_q < 0 || a->seqlen_k < 0)
+    return fail(FA2_E_VALUE, "unsupported backward tensor dimensions");
+  if ((a->which & 3) == 0) return fail(FA2_E_VALUE, "`which` selects no output");
+  if (packed && a->cu_seqlens_k == nullptr) return fail(FA2_E_VALUE, "packed backward needs cu_seqlens_k");
+  int device = 0;
+  cudaGetDevice(&device);
+  Runtime* rt = nullptr;
+  int rc = get_runtime(device, &rt);
+  if (rc != FA2_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const int64_t rows_q = packed ? a->total_q : a->seqlen_q;
+  const int64_t rows_k = packed ? a->total_k : a->seqlen_k;
+  const int64_t nbatch = packed ? 1 : a->batch;
+  const bool want_dq = (a->which & 1) != 0, want_dkv = (a->which & 2) != 0;
+  const int64_t n_dq = bwd_rows(a) * a->heads * d;
+  const int64_t n_dkv = (packed ? rows_k : static_cast<int64_t>(a->batch) * a->seqlen_k) * a->heads_k * d;
+  cudaError_t e;
+  if (rows_q == 0 || a->seqlen_q == 0 || rows_k == 0 || a->seqlen_k == 0) {
+    // Nothing attends: every gradient that exists is zero.
+    if (want_dq && n_dq > 0 && (e = cudaMemsetAsync(a->dq, 0, n_dq * 2, stream)) != cudaSuccess)
+      return fail(FA2_E_RUNTIME, "memset failed: %s", cudaGetErrorString(e));
+    if (want_dkv && n_dkv > 0) {
+      cudaMemsetAsync(a->dk, 0, n_dkv * 2, stream);
+      cudaMemsetAsync(a->dv, 0, n_dkv * 2, stream);
+    }
+    return FA2_OK;
+  }
+  if (want_dq) {
+    if (a->dq == nullptr || a->dq_accum == nullptr) return fail(FA2_E_VALUE, "dq and dq_accum must be non-null");
+    if (a->dq_accum_bytes < n_dq * 4) return fail(FA2_E_VALUE, "dq_accum is smaller than fa2_bwd_workspace_bytes()");
+    if (reinterpret_cast<uintptr_t>(a->dq_accum) % 16 || reinterpret_cast<uintptr_t>(a->dq) % 16)
+      return fail(FA2_E_VALUE, "dq and dq_accum must be 16-byte aligned");
+  }
+  if (a->dk == nullptr || a->dv == nullptr) return fail(FA2_E_VALUE, "dk and dv must be non-null");
+  if (a->lse == nullptr || a->delta == nullptr) return fail(FA2_E_VALUE, "lse and delta must be non-null");
+  const int ns = packed ? 2 : 3;
+  const int so = packed ? 1 : 0;
+  if ((rc = check_layout(a->q, a->q_stride + so, ns, "q")) != FA2_OK) return rc;
+  if ((rc = check_layout(a->k, a->k_stride + so, ns, "k")) != FA2_OK) return rc;
+  if ((rc = check_layout(a->v, a->v_stride + so, ns, "v")) != FA2_OK) return rc;
+  if ((rc = check_layout(a->dout, a->do_stride + so, ns, "dout")) != FA2_OK) return rc;
+  if (reinterpret_cast<uintptr_t>(a->dk) % 16 || reinterpret_cast<uintptr_t>(a->dv) % 16)
+    return fail(FA2_E_VALUE, "dk and dv must be 16-byte aligned");
+
+  fa2::BwdParams p;
+  memset(&p, 0, sizeof(p));
+  const int64_t hd = static_cast<int64_t>(a->heads) * d, hkd = static_cast<int64_t>(a->heads_k) * d;
+  if ((rc = make_map(&p.tm_q, a->q, a->dtype, 2, d, a->heads, rows_q, nbatch, a->q_stride[2], a->q_stride[1],
+                     a->q_stride[0], 64, 128, "q")) != FA2_OK) return rc;
+  if ((rc = make_map(&p.tm_do, a->dout, a->dtype, 2, d, a->heads, rows_q, nbatch, a->do_stride[2], a->do_stride[1],
+                     a->do_stride[0], 64, 128, "dout")) != FA2_OK) return rc;
+  if ((rc = make_map(&p.tm_k, a->k, a->dtype, 2, d, a->heads_k, rows_k, nbatch, a->k_stride[2], a->k_stride[1],
+                     a->k_stride[0], 64, 128, "k")) != FA2_OK) return rc;
+  if ((rc = make_map(&p.tm_v, a->v, a->dtype, 2, d, a->heads_k, rows_k, nbatch, a->v_stride[2], a->v_stride[1],
+                     a->v_stride[0], 64, 128, "v")) != FA2_OK) return rc;
+  if ((rc = make_map(&p.tm_dk, a->dk, a->dtype, 2, d, a->heads_k, rows_k, nbatch, d, hkd, rows_k * hkd, 64, 128,
+                     "dk")) != FA2_OK) return rc;
+  if ((rc = make_map(&p.tm_dv, a->dv, a->dtype, 2, d, a->heads_k, rows_k, nbatch, d, hkd, rows_k * hkd, 64, 128,
+                     "dv")) != FA2_OK) return rc;
+  if (want_dq) {
+    if ((rc = make_map(&p.tm_dqa, a->dq_accum, 2, 4, d, a->heads, rows_q, nbatch, d, hd, rows_q * hd, 32, 128,
+                       "dq_accum")) != FA2_OK) return rc;
+  } else {
+    p.tm_dqa = p.tm_q;
+  }
+  p.lse = a->lse;
+  p.delta = a->delta;
+  p.dk_ptr = a->dk;
+  p.dv_ptr = a->dv;
+  p.cu_q = a->cu_seqlens_q;
+  p.cu_k = a->cu_seqlens_k;
+  const int64_t sq_pad = (a->seqlen_q + 127) / 128 * 128;
+  if (packed) {
+    p.lse_head_stride = a->total_q;
+    p.lse_batch_stride = 0;
+    p.delta_head_stride = static_cast<int64_t>(a->total_q) + 128LL * a->batch;
+    p.delta_batch_stride = 0;
+    p.delta_seq_pad = 128;
+  } else {
+    p.lse_head_stride = a->seqlen_q;
+    p.lse_batch_stride = static_cast<int64_t>(a->heads) * a->seqlen_q;
+    p.delta_head_stride = sq_pad;
+    p.delta_batch_stride = static_cast<int64_t>(a->heads) * sq_pad;
+    p.delta_seq_pad = 0;
+  }
+  p.dkv_row_stride = hkd;
+  p.dkv_head_stride = d;
+  p.dkv_batch_stride = rows_k * hkd;
+  p.batch = a->batch;
+  p.heads = a->heads;
+  p.heads_k = a->heads_k;
+  p.group = a->heads / a->heads_k;
+  p.seqlen_q = a->seqlen_q;
+  p.seqlen_k = a->seqlen_k;
+  p.num_nblk = (a->seqlen_k + 127) / 128;
+  const Windows w = normalise_windows(a->window_left, a->window_right, a->causal != 0, a->seqlen_k, packed);
+  p.window_left = w.left;
+  p.window_right = w.right;
+  p.which = a->which;
+  p.scale = a->softmax_scale;
+  p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  p.status = rt->status;
+
+  if (want_dq && (e = cudaMemsetAsync(a->dq_accum, 0, n_dq * 4, stream)) != cudaSuccess)
+    return fail(FA2_E_RUNTIME, "memset failed: %s", cudaGetErrorString(e));
+  if ((e = fa2::launch_bwd(p, d, a->dtype == FA2_BF16, stream)) != cudaSuccess)
+    return fail(FA2_E_RUNTIME, "backward launch failed: %s", cudaGetErrorString(e));
+  if (want_dq && (e = fa2::launch_dq_convert(static_cast<const float*>(a->dq_accum), a->dq, n_dq, a->softmax_scale,
+                                             a->dtype == FA2_BF16, stream)) != cudaSuccess)
+    return fail(FA2_E_RUNTIME, "dq convert launch failed: %s", cudaGetErrorString(e));
+  return FA2_OK;
+}
+
 }  // namespace
 
 extern "C" {
+
+int fa2_bwd_preprocess(const fa2_bwd_preprocess_args* args, void* stream) { return bwd_preprocess_impl(args, stream); }
+
+int64_t fa2_bwd_workspace_bytes(const fa2_bwd_args* args) {
+  if (args == nullptr || (args->which & 1) == 0) return 0;
+  return bwd_rows(args) * args->heads * args->head_dim * 4;
+}
+
+int fa2_bwd(const fa2_bwd_args* args, void* stream) { return bwd_impl(args, stream); }
+
 
 int fa2_fwd(const fa2_fwd_args* args, void* stream) { return fwd_common(args, stream, false); }
 

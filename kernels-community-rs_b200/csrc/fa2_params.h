@@ -43,4 +43,38 @@ struct FwdParams {
   int* status;                         // device status word (0 = ok)
 };
 
+struct BwdParams {
+  CUtensorMap tm_q, tm_k, tm_v, tm_do;  // 16-bit inputs, box (64, 1, 128, 1)
+  CUtensorMap tm_dk, tm_dv;             // 16-bit outputs, box (64, 1, 128, 1)
+  CUtensorMap tm_dqa;                   // fp32 dQ accumulator, box (32, 1, 128, 1)
+  const float* lse;
+  const float* delta;
+  void* dk_ptr;
+  void* dv_ptr;
+  const int32_t* cu_q;
+  const int32_t* cu_k;
+  int64_t lse_head_stride, lse_batch_stride;
+  int64_t delta_head_stride, delta_batch_stride;
+  int64_t dkv_row_stride, dkv_head_stride, dkv_batch_stride;  // elements
+  int delta_seq_pad;                    // 128 in packed mode (sequence b starts at cu_q[b] + 128 b), else 0
+  int batch, heads, heads_k, group, seqlen_q, seqlen_k;
+  int num_nblk;                         // ceil(seqlen_k / 128)
+  int window_left, window_right;
+  int which;                            // bit 0: dQ, bit 1: dK and dV
+  float scale, scale_log2;
+  int* status;
+};
+
+struct PreprocessParams {
+  const void* dout;
+  const void* out;
+  float* delta;
+  const int32_t* cu_q;
+  int64_t do_batch_stride, do_row_stride, do_head_stride;
+  int64_t o_batch_stride, o_row_stride, o_head_stride;
+  int64_t delta_head_stride, delta_batch_stride;
+  int batch, heads, seqlen_q, seqlen_pad, head_dim;
+  int bf16;
+};
+
 }  // namespace fa2

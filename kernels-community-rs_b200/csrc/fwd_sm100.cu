@@ -41,7 +41,7 @@ struct FwdCfg {
   static constexpr int kQOff = 0;
   static constexpr int kKVOff = 2 * kTileBytes;
   static constexpr int kBarOff = kKVOff + kSlots * kTileBytes;
-  static constexpr int kNumBars = 2 * kSlots + 14;
+  static constexpr int kNumBars = 2 * kSlots + 16;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;  // tmem slot, abort flag
   static constexpr int kStatOff = kMiscOff + 32;           // l and m exchange: [2 stages][128][2]
   static constexpr int kSmemBytes = kStatOff + 2 * 128 * 2 * 4 + 1024;  // + alignment slack
@@ -137,6 +137,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   uint64_t* pv_done = q_full + 8;
   uint64_t* sm_final = q_full + 10;
   uint64_t* o_free = q_full + 12;
+  uint64_t* epi_full = q_full + 14;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::kMiscOff + 8);
   float* s_stat = reinterpret_cast<float*>(smem + Cfg::kStatOff);
@@ -160,6 +161,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
       mbar_init(&pv_done[s], 1);
       mbar_init(&sm_final[s], kBlockM);
       mbar_init(&o_free[s], kBlockM);
+      mbar_init(&epi_full[s], kBlockM);
     }
     mbar_fence_init();
   }
@@ -313,6 +315,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint32_t n_tile = 0;
     uint32_t n_pv[2] = {0, 0};
+    uint32_t n_epi[2] = {0, 0};
     bool ok = true;
     for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
       const Tile ti = get_tile(p, t);
@@ -373,17 +376,18 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           p.lse_ptr[ti.bq * p.lse_batch_stride + ti.h * p.lse_head_stride + ti.q_row0 + row] = lse;
         }
         if (iters > 0 && tma_store) {
+          // All 128 rows staged -> one thread stores the tile.
           fence_proxy_async_smem();
-          named_bar_sync(1, kBlockM);
+          mbar_arrive(&epi_full[s]);
           if (row_in == 0) {
+            if (!mbar_wait(&epi_full[s], n_epi[s] & 1, ctl, kWaitEpiFinal)) { ok = false; break; }
 #pragma unroll
             for (int a = 0; a < Cfg::kAtoms; ++a)
               tma_store_4d(&p.tm_o, stage_smem + a * (kBlockM * 128), a * 64, ti.h, ti.q_row0 + r_lo, ti.bq);
             tma_commit_group();
             tma_wait_group_read<0>();
           }
-        } else {
-          named_bar_sync(1, kBlockM);
+          ++n_epi[s];
         }
         if (row_in == 0) mbar_arrive(&q_empty[s]);
       }

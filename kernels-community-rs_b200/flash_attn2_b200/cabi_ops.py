@@ -138,3 +138,85 @@ def device_status(device=None) -> int:
     """Synchronises and returns the kernels' status word (0 = ok); see fa2_device_status."""
     idx = torch.cuda.current_device() if device is None else torch.device(device).index
     return _cabi.load().fa2_device_status(idx)
+
+
+def bwd_preprocess(dout, out, *, cu_seqlens_q=None, max_seqlen_q=None):
+    """delta = rowsum(dO * O) in fp32: [B, H, ceil(Sq/128)*128], or packed [H, total_q + 128*batch]."""
+    _require_cuda(dout, out)
+    lib = _cabi.load()
+    if dout.shape != out.shape or dout.dtype != out.dtype or dout.device != out.device:
+        raise ValueError("dout and out must share shape, dtype and device")
+    _check_last_stride("dout", dout)
+    _check_last_stride("out", out)
+    a = _cabi.BwdPreprocessArgs()
+    a.dout, a.out = dout.data_ptr(), out.data_ptr()
+    a.dtype = _dtype_code(dout)
+    if cu_seqlens_q is None:
+        b, sq, h, d = out.shape
+        delta = torch.empty((b, h, (sq + 127) // 128 * 128), dtype=torch.float32, device=out.device)
+        a.batch, a.seqlen_q = b, sq
+    else:
+        total_q, h, d = out.shape
+        b = cu_seqlens_q.numel() - 1
+        delta = torch.zeros((h, total_q + 128 * b), dtype=torch.float32, device=out.device)
+        a.batch, a.seqlen_q = b, int(max_seqlen_q)
+        a.cu_seqlens_q, a.total_q = cu_seqlens_q.data_ptr(), total_q
+    a.delta = delta.data_ptr()
+    a.heads, a.head_dim = h, d
+    a.do_stride, a.o_stride = _strides3(dout), _strides3(out)
+    with torch.cuda.device(out.device):
+        _cabi.check(lib.fa2_bwd_preprocess(C.byref(a), _stream(out)))
+    return delta
+
+
+def bwd(q, k, v, dout, lse, delta, *, softmax_scale=None, causal=False, window_left=-1, window_right=-1,
+        which=3, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=None, max_seqlen_k=None, dq_accum=None):
+    """dQ, dK, dV (input dtype, contiguous). `which`: bit 0 = dQ, bit 1 = dK and dV."""
+    _require_cuda(q, k, v, dout, lse, delta)
+    lib = _cabi.load()
+    if k.dtype != q.dtype or v.dtype != q.dtype or dout.dtype != q.dtype:
+        raise TypeError("q, k, v, dout must share dtype (all f16 or all bf16)")
+    if dout.shape != q.shape or v.shape != k.shape:
+        raise ValueError("dout must match q and v must match k")
+    for name, t in (("q", q), ("k", k), ("v", v), ("dout", dout)):
+        _check_last_stride(name, t)
+    if lse.dtype != torch.float32 or delta.dtype != torch.float32 or not lse.is_contiguous() or not delta.is_contiguous():
+        raise ValueError("lse and delta must be contiguous float32")
+    a = _cabi.BwdArgs()
+    packed = cu_seqlens_q is not None
+    if packed:
+        total_q, h, d = q.shape
+        total_k, hk = k.shape[0], k.shape[1]
+        b = cu_seqlens_q.numel() - 1
+        a.batch, a.seqlen_q, a.seqlen_k = b, int(max_seqlen_q), int(max_seqlen_k)
+        a.cu_seqlens_q, a.cu_seqlens_k = cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr()
+        a.total_q, a.total_k = total_q, total_k
+        if tuple(lse.shape) != (h, total_q) or tuple(delta.shape) != (h, total_q + 128 * b):
+            raise ValueError("packed lse must be [H, total_q] and delta [H, total_q + 128*batch]")
+    else:
+        b, sq, h, d = q.shape
+        sk, hk = k.shape[1], k.shape[2]
+        a.batch, a.seqlen_q, a.seqlen_k = b, sq, sk
+        if tuple(lse.shape) != (b, h, sq) or tuple(delta.shape) != (b, h, (sq + 127) // 128 * 128):
+            raise ValueError("lse must be [B, H, Sq] and delta [B, H, ceil(Sq/128)*128]")
+    dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+    dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+    a.q, a.k, a.v, a.dout = q.data_ptr(), k.data_ptr(), v.data_ptr(), dout.data_ptr()
+    a.lse, a.delta = lse.data_ptr(), delta.data_ptr()
+    a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    a.dtype = _dtype_code(q)
+    a.heads, a.heads_k, a.head_dim = h, hk, d
+    a.q_stride, a.k_stride, a.v_stride, a.do_stride = _strides3(q), _strides3(k), _strides3(v), _strides3(dout)
+    a.softmax_scale = float(softmax_scale) if softmax_scale is not None else 1.0 / (d ** 0.5)
+    a.causal = int(bool(causal))
+    a.window_left, a.window_right = int(window_left), int(window_right)
+    a.which = int(which)
+    need = lib.fa2_bwd_workspace_bytes(C.byref(a))
+    if need > 0:
+        if dq_accum is None:
+            dq_accum = torch.empty(need // 4, dtype=torch.float32, device=q.device)
+        a.dq_accum, a.dq_accum_bytes = dq_accum.data_ptr(), dq_accum.numel() * 4
+    with torch.cuda.device(q.device):
+        _cabi.check(lib.fa2_bwd(C.byref(a), _stream(q)))
+    return dq, dk, dv
