@@ -1,0 +1,280 @@
+"""Headline benchmark: FA2 forward + backward, bf16, B16 H16 S2048 D128 causal, on N B200s.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one forward and one backward pass (delta preprocess, dQ/dK/dV kernel, dQ convert) over
+one batch of seeded synthetic inputs. With N > 1 (launched through torch.distributed.run) every rank
+runs the same workload on its own inputs (independent (batch, head) units, no collective on the data
+path), so the job is weak-scaled: value = FLOPs of all ranks / max-over-ranks device time.
+Rank 0 prints one JSON line.
+
+`--impl reference` times the reference path that can run here: the crate's test-harness naive
+attention (fp32, CPU) restated in oracle/attention_oracle.py, on a bounded sample of the same
+workload, with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "kernels-community-rs_b200"))
+
+import torch  # noqa: E402
+
+B, H, S, D = 16, 16, 2048, 128
+CAUSAL = True
+FWD_FLOPS = 4.0 * B * H * S * S * D * 0.5
+BWD_FLOPS = 2.5 * FWD_FLOPS
+METRIC = "FA2 fwd/bwd TFLOP/s bf16 B16 H16 S2048 D128 causal; % of B200 dense peak"
+WORKLOAD = "FA2 forward+backward, causal, B=16, H_q=H_kv=16, S=2048, D=128, bf16 (BASELINE configs[1]+[2])"
+
+
+def measured_peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        d = json.loads(f.read_text())
+        return d.get("bf16_tflops", 1590.0), d.get("bf16_tflops_sustained"), "measured"
+    return 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self._stop = index, [], threading.Event()
+        self._t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([x.strip() for x in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._t.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        sm = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for s in self.samples for n, v in zip(names, s[2:6]) if v.lower().startswith("active")})
+        mx = max((int(s[1]) for s in self.samples if s[1].isdigit()), default=None)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": reasons,
+                "samples": len(self.samples)}
+
+
+def make_inputs(seed, pin=False):
+    g = torch.Generator().manual_seed(seed)
+    ts = [torch.randn(B, S, H, D, generator=g).to(torch.bfloat16) for _ in range(4)]  # q, k, v, dO
+    return [t.pin_memory() for t in ts] if pin else ts
+
+
+def cpu_reference_sample(pairs, threads):
+    """fp32 naive attention forward + explicit backward on `pairs` (batch, head) units; seconds."""
+    from oracle.attention_oracle import attention_backward, attention_forward
+
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(1)
+    q, k, v, do = [torch.randn(1, S, pairs, D, generator=g).to(torch.bfloat16) for _ in range(4)]
+    t0 = time.perf_counter()
+    out, lse = attention_forward(q, k, v, causal=CAUSAL)
+    attention_backward(q, k, v, do, causal=CAUSAL, out=out, lse=lse)
+    return time.perf_counter() - t0
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    pairs = 8
+    cpu_reference_sample(1, threads)  # warm-up (also pages torch in)
+    for _ in range(max(args.warmup - 1, 0)):
+        cpu_reference_sample(pairs, threads)
+    times = [cpu_reference_sample(pairs, threads) for _ in range(args.steps)]
+    t = sum(times) / len(times)
+    flops = (FWD_FLOPS + BWD_FLOPS) * pairs / (B * H)
+    value = flops / t / 1e12
+    sample = f"{pairs} of the {B * H} (batch, head) units per step, forward + backward, fp32 on the host CPU"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank, world):
+    import torch.distributed as dist
+    from flash_attn2_b200 import cabi_ops as ops
+    import flash_attn2_b200 as plugin
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    host = make_inputs(1 + rank, pin=True)
+    q, k, v, do = [t.to(dev, non_blocking=True) for t in host]
+    acc = torch.empty(B * S * H * D, dtype=torch.float32, device=dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+    k0, k1 = ev(), ev()
+    k0.record(), k1.record()  # materialise the handles
+    torch.cuda.synchronize()
+
+    def fwd_only():
+        return ops.fwd(q, k, v, causal=CAUSAL)
+
+    def bwd_only(o, lse, events=None):
+        delta = ops.bwd_preprocess(do, o)
+        return ops.bwd(q, k, v, do, lse, delta, causal=CAUSAL, dq_accum=acc, kernel_events=events)
+
+    def step():
+        o, lse = fwd_only()
+        return bwd_only(o, lse)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = ev(), ev()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / n
+
+    for _ in range(args.warmup):
+        step()
+    with ClockSampler(local) as clocks:
+        ms_step = timed(step, args.steps)
+        # Per-kernel figures for the roofline and the per-pass targets.
+        ms_fwd = timed(fwd_only, args.steps)
+        o, lse = fwd_only()
+        ms_bwd = timed(lambda: bwd_only(o, lse), args.steps)
+        kt = []
+        for _ in range(args.steps):
+            bwd_only(o, lse, events=(k0, k1))
+            torch.cuda.synchronize()
+            kt.append(k0.elapsed_time(k1))
+        ms_bwd_kernel = sum(kt) / len(kt)
+    status = ops.device_status()
+    if status != 0:
+        raise RuntimeError(f"kernel pipeline reported a stalled wait (status {status})")
+
+    # End to end through the operator (plugin) API with host buffers: H2D of q, k, v, dO, the
+    # tvm-ffi forward + backward, D2H of O, LSE, dQ, dK, dV.
+    outs_host = [torch.empty_like(host[0]).pin_memory() for _ in range(4)]
+    lse_host = torch.empty(B, H, S, dtype=torch.float32).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host)
+    d2h = sum(t.numel() * t.element_size() for t in outs_host) + lse_host.numel() * 4
+
+    def e2e_step():
+        qd, kd, vd, dod = [t.to(dev, non_blocking=True) for t in host]
+        out, lse_d, _, _ = plugin.fwd(qd, kd, vd, is_causal=CAUSAL)
+        dq, dk, dv, _ = plugin.bwd(dod, qd, kd, vd, out, lse_d, is_causal=CAUSAL)
+        for dst, src in zip(outs_host, (out, dq, dk, dv)):
+            dst.copy_(src, non_blocking=True)
+        lse_host.copy_(lse_d, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step()
+    ms_e2e = timed(e2e_step, e2e_steps)
+
+    if rank == 0:
+        peak, sustained, peak_kind = measured_peaks()
+        total = (FWD_FLOPS + BWD_FLOPS) * world
+        tf = lambda fl, ms: fl / ms / 1e9  # noqa: E731
+        traffic = None
+        tfile = ROOT / "profiles" / "ncu_traffic.json"
+        if tfile.exists():
+            traffic = json.loads(tfile.read_text()).get("bwd_kernel_dram_bytes_per_launch")
+        cpu = None
+        if world == 1:
+            threads = os.cpu_count() or 1
+            pairs = 16
+            cpu_reference_sample(1, threads)
+            t = cpu_reference_sample(pairs, threads)
+            cpu = {"value": (FWD_FLOPS + BWD_FLOPS) * pairs / (B * H) / t / 1e12, "unit": "TFLOP/s", "cores": threads,
+                   "kind": "port",
+                   "sample": f"{pairs} of the {B * H} (batch, head) units, forward + backward, fp32 on the host CPU"}
+        achieved = tf(BWD_FLOPS, ms_bwd_kernel)
+        line = {
+            "metric": METRIC, "value": tf(total, ms_step), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "global_batch": B * world, "sharding": "independent batches per GPU",
+                       "l2": "inputs and outputs (1.1 GB per step) exceed the 126 MB L2"},
+            "detail": {
+                "fwd_tflops": tf(FWD_FLOPS * world, ms_fwd), "bwd_tflops": tf(BWD_FLOPS * world, ms_bwd),
+                "fwd_ms": ms_fwd, "bwd_ms": ms_bwd, "bwd_kernel_ms": ms_bwd_kernel,
+                "fwd_frac_of_peak": tf(FWD_FLOPS, ms_fwd) / peak, "bwd_frac_of_peak": tf(BWD_FLOPS, ms_bwd) / peak,
+                "peak_tflops": peak, "peak_sustained_tflops": sustained, "peak_kind": peak_kind,
+            },
+            "roofline": {"kernel": "bwd_kernel<128, bf16>", "bound": "tensor", "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind},
+            "roofline_fwd": {"kernel": "fwd_kernel<128, bf16>", "bound": "tensor", "achieved": tf(FWD_FLOPS, ms_fwd),
+                             "peak": peak, "unit": "TFLOP/s", "frac": tf(FWD_FLOPS, ms_fwd) / peak},
+            "cpu_baseline": cpu,
+            "e2e": {"value": tf(total, ms_e2e), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
+            "gpu_launches": 4 * args.steps,
+            "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_ours(args, rank, world)
+
+
+if __name__ == "__main__":
+    main()

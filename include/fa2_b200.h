@@ -58,6 +58,7 @@ typedef struct fa2_fwd_args {
   const int32_t* cu_seqlens_q;
   const int32_t* cu_seqlens_k;
   int32_t total_q, total_k;
+  int32_t zero_tensors; /* packed mode: clear out (0) and LSE (-inf) first, as the reference's flag does */
 } fa2_fwd_args;
 
 /* Dense forward. Replaces launch_forward + flash_attn_fwd of the reference
@@ -115,6 +116,10 @@ typedef struct fa2_bwd_args {
   const int32_t* cu_seqlens_q;
   const int32_t* cu_seqlens_k;
   int32_t total_q, total_k;
+  /* Optional cudaEvent_t handles recorded on `stream` right before and right after the main
+   * dQ/dK/dV kernel (not the memset / convert around it), for per-kernel timing. May be NULL. */
+  void* ev_kernel_start;
+  void* ev_kernel_stop;
 } fa2_bwd_args;
 FA2_API int64_t fa2_bwd_workspace_bytes(const fa2_bwd_args* args);
 FA2_API int fa2_bwd(const fa2_bwd_args* args, void* stream);

@@ -142,6 +142,11 @@ __global__ void fill_empty_kernel(uint16_t* out, float* lse, int64_t rows, int h
   lse[b * lse_batch_stride + h * lse_head_stride + s] = lse_value;
 }
 
+__global__ void fill_f32_kernel(float* dst, int64_t n, float value) {
+  const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (i < n) dst[i] = value;
+}
+
 int fwd_common(const fa2_fwd_args* a, void* stream_v, bool packed) {
   if (a == nullptr) return fail(FA2_E_VALUE, "args is null");
   if (a->dtype != FA2_F16 && a->dtype != FA2_BF16) return fail(FA2_E_TYPE, "q, k, v must be float16 or bfloat16");
@@ -195,6 +200,12 @@ int fwd_common(const fa2_fwd_args* a, void* stream_v, bool packed) {
   }
   if (a->out == nullptr || a->lse == nullptr) return fail(FA2_E_VALUE, "out and lse must be non-null");
 
+  if (packed && a->zero_tensors && a->seqlen_k != 0 && rows_k != 0) {
+    // zero_tensors of the reference: out = 0, LSE = -inf before the kernel (varlen/mod.rs:419-444).
+    cudaMemsetAsync(a->out, 0, static_cast<size_t>(rows_q) * a->heads * d * 2, stream);
+    const int64_t n = rows_q * a->heads;
+    fill_f32_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(a->lse, n, -INFINITY);
+  }
   if (rows_k == 0 || a->seqlen_k == 0) {
     // No keys at all: O = 0, LSE = +inf (forward/mod.rs:548-582).
     const int64_t n = rows_q * nbatch * a->heads;
@@ -294,6 +305,8 @@ int bwd_preprocess_impl(const fa2_bwd_preprocess_args* a, void* stream_v) {
     p.delta_head_stride = p.seqlen_pad;
     p.delta_batch_stride = static_cast<int64_t>(a->heads) * p.seqlen_pad;
   }
+  if (packed)  // the 128-row gaps between packed sequences read as zero
+    cudaMemsetAsync(a->delta, 0, static_cast<size_t>(p.delta_head_stride) * a->heads * 4, static_cast<cudaStream_t>(stream_v));
   cudaError_t e = fa2::launch_bwd_preprocess(p, static_cast<cudaStream_t>(stream_v));
   if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "preprocess launch failed: %s", cudaGetErrorString(e));
   return FA2_OK;
@@ -418,8 +431,10 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
 
   if (want_dq && (e = cudaMemsetAsync(a->dq_accum, 0, n_dq * 4, stream)) != cudaSuccess)
     return fail(FA2_E_RUNTIME, "memset failed: %s", cudaGetErrorString(e));
-  if ((e = fa2::launch_bwd(p, d, a->dtype == FA2_BF16, stream)) != cudaSuccess)
-    return fail(FA2_E_RUNTIME, "backward launch failed: %s", cudaGetErrorString(e));
+  if (a->ev_kernel_start != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_kernel_start), stream);
+  e = fa2::launch_bwd(p, d, a->dtype == FA2_BF16, stream);
+  if (a->ev_kernel_stop != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_kernel_stop), stream);
+  if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "backward launch failed: %s", cudaGetErrorString(e));
   if (want_dq && (e = fa2::launch_dq_convert(static_cast<const float*>(a->dq_accum), a->dq, n_dq, a->softmax_scale,
                                              a->dtype == FA2_BF16, stream)) != cudaSuccess)
     return fail(FA2_E_RUNTIME, "dq convert launch failed: %s", cudaGetErrorString(e));

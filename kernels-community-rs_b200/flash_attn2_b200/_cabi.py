@@ -25,7 +25,7 @@ class FwdArgs(C.Structure):
         ("softmax_scale", C.c_float), ("causal", C.c_int32),
         ("window_left", C.c_int32), ("window_right", C.c_int32), ("softcap", C.c_float),
         ("cu_seqlens_q", C.c_void_p), ("cu_seqlens_k", C.c_void_p),
-        ("total_q", C.c_int32), ("total_k", C.c_int32),
+        ("total_q", C.c_int32), ("total_k", C.c_int32), ("zero_tensors", C.c_int32),
     ]
 
 
@@ -52,6 +52,7 @@ class BwdArgs(C.Structure):
         ("window_left", C.c_int32), ("window_right", C.c_int32), ("which", C.c_int32),
         ("cu_seqlens_q", C.c_void_p), ("cu_seqlens_k", C.c_void_p),
         ("total_q", C.c_int32), ("total_k", C.c_int32),
+        ("ev_kernel_start", C.c_void_p), ("ev_kernel_stop", C.c_void_p),
     ]
 
 

@@ -170,8 +170,11 @@ def bwd_preprocess(dout, out, *, cu_seqlens_q=None, max_seqlen_q=None):
 
 
 def bwd(q, k, v, dout, lse, delta, *, softmax_scale=None, causal=False, window_left=-1, window_right=-1,
-        which=3, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=None, max_seqlen_k=None, dq_accum=None):
-    """dQ, dK, dV (input dtype, contiguous). `which`: bit 0 = dQ, bit 1 = dK and dV."""
+        which=3, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=None, max_seqlen_k=None, dq_accum=None,
+        kernel_events=None):
+    """dQ, dK, dV (input dtype, contiguous). `which`: bit 0 = dQ, bit 1 = dK and dV.
+
+    `kernel_events`: optional pair of torch.cuda.Event recorded around the main kernel only."""
     _require_cuda(q, k, v, dout, lse, delta)
     lib = _cabi.load()
     if k.dtype != q.dtype or v.dtype != q.dtype or dout.dtype != q.dtype:
@@ -212,6 +215,8 @@ def bwd(q, k, v, dout, lse, delta, *, softmax_scale=None, causal=False, window_l
     a.causal = int(bool(causal))
     a.window_left, a.window_right = int(window_left), int(window_right)
     a.which = int(which)
+    if kernel_events is not None:
+        a.ev_kernel_start, a.ev_kernel_stop = kernel_events[0].cuda_event, kernel_events[1].cuda_event
     need = lib.fa2_bwd_workspace_bytes(C.byref(a))
     if need > 0:
         if dq_accum is None:
