@@ -1,0 +1,163 @@
+"""GPU parity of the backward path (delta preprocess, dQ/dK/dV) against the CPU oracle.
+
+Shapes follow the reference's backward tests (flash-attn2-rs/tests/test_gold.py:269-363: MHA/GQA,
+causal, odd lengths, strided inputs, delta parity at 2e-5) plus BASELINE configs[2] at full size.
+"""
+import pytest
+import torch
+
+from tests._cases import BWD_TOL, make_qkv
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    ("full-s128", (1, 2, 2, 128, 128, 128), {}),
+    ("causal-s256", (2, 4, 4, 256, 256, 128), dict(causal=True)),
+    ("full-s256", (2, 4, 4, 256, 256, 128), {}),
+    ("causal-gqa-h8-hk2", (2, 8, 2, 256, 256, 128), dict(causal=True)),
+    ("mqa-h4-hk1", (1, 4, 1, 192, 192, 128), {}),
+    ("odd-causal-s333", (2, 4, 4, 333, 333, 128), dict(causal=True)),
+    ("causal-sq320-sk256", (1, 4, 4, 320, 256, 128), dict(causal=True)),
+    ("full-sq128-sk256", (1, 4, 4, 128, 256, 128), {}),
+    ("window-wl64-wr64", (1, 4, 4, 256, 256, 128), dict(window_left=64, window_right=64)),
+    ("local-causal-wl64", (1, 4, 4, 300, 300, 128), dict(causal=True, window_left=64)),
+    ("custom-scale", (1, 4, 4, 256, 256, 128), dict(causal=True, softmax_scale=0.05)),
+    ("d64-causal-gqa", (2, 4, 2, 512, 512, 64), dict(causal=True)),
+    ("d64-odd", (1, 2, 2, 200, 333, 64), {}),
+    ("s1024-causal", (1, 4, 4, 1024, 1024, 128), dict(causal=True)),
+]
+
+
+def _run(q, k, v, do, **opt):
+    from flash_attn2_b200 import cabi_ops as ops
+
+    qc, kc, vc, doc = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    out, lse = ops.fwd(qc, kc, vc, **opt)
+    delta = ops.bwd_preprocess(doc, out)
+    dq, dk, dv = ops.bwd(qc, kc, vc, doc, lse, delta, **opt)
+    assert ops.device_status() == 0
+    return out, lse, delta, dq, dk, dv
+
+
+def _close(got, ref, dtype, name):
+    tol = BWD_TOL[dtype]
+    got = got.float().cpu()
+    assert torch.isfinite(got).all(), name
+    torch.testing.assert_close(got, ref, atol=tol["atol"], rtol=tol["rtol"], msg=lambda m: f"{name}: {m}")
+
+
+@pytest.mark.parametrize("name,shape,opt", CASES, ids=[c[0] for c in CASES])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["f16", "bf16"])
+def test_backward_parity_cabi(name, shape, opt, dtype):
+    from oracle.attention_oracle import attention_backward
+
+    b, h, hk, sq, sk, d = shape
+    q, k, v, do = make_qkv(2, b, h, hk, sq, sk, d, dtype, with_do=True)
+    out, lse, delta, dq, dk, dv = _run(q, k, v, do, **opt)
+    dq_ref, dk_ref, dv_ref, delta_ref = attention_backward(q, k, v, do, out=out.float().cpu(), **opt)
+    torch.testing.assert_close(delta.cpu(), delta_ref, atol=2e-5, rtol=1e-5)
+    _close(dq, dq_ref, dtype, "dq")
+    _close(dk, dk_ref, dtype, "dk")
+    _close(dv, dv_ref, dtype, "dv")
+
+
+def test_backward_rows_without_keys_get_zero_gradient():
+    """Causal with Sq > Sk: the first Sq - Sk rows see no key (LSE = +inf) and must get dQ = 0."""
+    q, k, v, do = make_qkv(3, 1, 2, 2, 384, 256, 128, torch.float16, with_do=True)
+    out, lse, delta, dq, dk, dv = _run(q, k, v, do, causal=True)
+    assert torch.isposinf(lse[:, :, :128]).all()
+    assert (dq[:, :128] == 0).all()
+    assert torch.isfinite(dk.float()).all() and torch.isfinite(dv.float()).all()
+
+
+def test_backward_dq_only_and_dkv_only_match_all():
+    from flash_attn2_b200 import cabi_ops as ops
+
+    q, k, v, do = [t.cuda() for t in make_qkv(4, 2, 4, 2, 256, 256, 128, torch.bfloat16, with_do=True)]
+    out, lse = ops.fwd(q, k, v, causal=True)
+    delta = ops.bwd_preprocess(do, out)
+    dq, dk, dv = ops.bwd(q, k, v, do, lse, delta, causal=True, which=3)
+    dq1, _, _ = ops.bwd(q, k, v, do, lse, delta, causal=True, which=1)
+    _, dk2, dv2 = ops.bwd(q, k, v, do, lse, delta, causal=True, which=2)
+    assert ops.device_status() == 0
+    assert torch.equal(dk, dk2) and torch.equal(dv, dv2)  # dK/dV never use atomics
+    torch.testing.assert_close(dq1.float(), dq.float(), atol=2e-2, rtol=2e-2)  # fp32 add order may differ
+
+
+def test_backward_strided_inputs():
+    """Head-sliced views of larger tensors (test_gold.py:269-310 uses strided backward inputs)."""
+    from flash_attn2_b200 import cabi_ops as ops
+    from oracle.attention_oracle import attention_backward
+
+    q, k, v, do = make_qkv(5, 1, 8, 8, 256, 256, 128, torch.float16, with_do=True)
+    qc, kc, vc, doc = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    sl = slice(2, 6)
+    out, lse = ops.fwd(qc[:, :, sl], kc[:, :, sl], vc[:, :, sl], causal=True)
+    delta = ops.bwd_preprocess(doc[:, :, sl], out)
+    dq, dk, dv = ops.bwd(qc[:, :, sl], kc[:, :, sl], vc[:, :, sl], doc[:, :, sl], lse, delta, causal=True)
+    dq_ref, dk_ref, dv_ref, _ = attention_backward(q[:, :, sl], k[:, :, sl], v[:, :, sl], do[:, :, sl], causal=True,
+                                                   out=out.float().cpu())
+    _close(dq, dq_ref, torch.float16, "dq")
+    _close(dk, dk_ref, torch.float16, "dk")
+    _close(dv, dv_ref, torch.float16, "dv")
+
+
+def test_backward_through_tvm_ffi_ops_and_autograd():
+    """bwd() returns [dQ, dK, dV, softmax_d]; deterministic=True takes the bwd_dq + bwd_dkv pair;
+    flash_attn_func differentiates through both."""
+    import flash_attn2_b200 as fa
+    from oracle.attention_oracle import attention_backward
+
+    q, k, v, do = make_qkv(6, 2, 8, 2, 256, 256, 128, torch.bfloat16, with_do=True)
+    qc, kc, vc, doc = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    out, lse, _, _ = fa.fwd(qc, kc, vc, is_causal=True)
+    dq_ref, dk_ref, dv_ref, delta_ref = attention_backward(q, k, v, do, causal=True, out=out.float().cpu())
+    for det in (False, True):
+        dq, dk, dv, delta = fa.bwd(doc, qc, kc, vc, out, lse, is_causal=True, deterministic=det)
+        torch.testing.assert_close(delta.cpu(), delta_ref, atol=2e-5, rtol=1e-5)
+        _close(dq, dq_ref, torch.bfloat16, "dq")
+        _close(dk, dk_ref, torch.bfloat16, "dk")
+        _close(dv, dv_ref, torch.bfloat16, "dv")
+    qa, ka, va = (t.clone().requires_grad_() for t in (qc, kc, vc))
+    fa.flash_attn_func(qa, ka, va, causal=True).backward(doc)
+    _close(qa.grad, dq_ref, torch.bfloat16, "dq")
+    _close(ka.grad, dk_ref, torch.bfloat16, "dk")
+    _close(va.grad, dv_ref, torch.bfloat16, "dv")
+    with pytest.raises((RuntimeError, ValueError)):
+        fa.bwd(doc, qc, kc, vc, out, lse[:, :, :-1].contiguous(), is_causal=True)
+
+
+def test_config3_full_size_slices_and_properties():
+    """BASELINE configs[2] (B16 H16 S2048 D128 bf16 causal, dO from seed 2) at full size: oracle on
+    sampled (batch, head) units; dV and dK/dQ are linear in dO; the last key's dK/dV only see the
+    last query row."""
+    from flash_attn2_b200 import cabi_ops as ops
+    from oracle.attention_oracle import attention_backward
+
+    g1, g2 = torch.Generator().manual_seed(1), torch.Generator().manual_seed(2)
+    q, k, v = [torch.randn(16, 2048, 16, 128, generator=g1).to(torch.bfloat16) for _ in range(3)]
+    do = torch.randn(16, 2048, 16, 128, generator=g2).to(torch.bfloat16)
+    qc, kc, vc, doc = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    out, lse = ops.fwd(qc, kc, vc, causal=True)
+    delta = ops.bwd_preprocess(doc, out)
+    dq, dk, dv = ops.bwd(qc, kc, vc, doc, lse, delta, causal=True)
+    assert ops.device_status() == 0
+    for t in (dq, dk, dv):
+        assert torch.isfinite(t.float()).all()
+    for b, h in [(0, 0), (9, 3), (15, 15)]:
+        sl = (slice(b, b + 1), slice(None), slice(h, h + 1))
+        dq_ref, dk_ref, dv_ref, delta_ref = attention_backward(q[sl], k[sl], v[sl], do[sl], causal=True,
+                                                               out=out[sl].float().cpu())
+        torch.testing.assert_close(delta[b:b + 1, h:h + 1].cpu(), delta_ref, atol=2e-5, rtol=1e-5)
+        _close(dq[sl], dq_ref, torch.bfloat16, "dq")
+        _close(dk[sl], dk_ref, torch.bfloat16, "dk")
+        _close(dv[sl], dv_ref, torch.bfloat16, "dv")
+    # key S-1 is visible to query S-1 only, with P = softmax weight p: dV[S-1] = p * dO[S-1]
+    p_last = torch.exp((qc[:, -1].float() * kc[:, -1].float()).sum(-1) / 128 ** 0.5 - lse[:, :, -1])
+    torch.testing.assert_close(dv[:, -1].float(), p_last.unsqueeze(-1) * doc[:, -1].float(), atol=2e-3, rtol=2e-2)
+    # linearity in dO (delta scales too)
+    delta2 = ops.bwd_preprocess(doc * 2, out)
+    dq2, dk2, dv2 = ops.bwd(qc, kc, vc, doc * 2, lse, delta2, causal=True)
+    torch.testing.assert_close(dv2.float(), dv.float() * 2, atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(dk2.float(), dk.float() * 2, atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(dq2.float(), dq.float() * 2, atol=2e-2, rtol=2e-2)
