@@ -4,14 +4,18 @@
 // rows of one (batch, head): two 128-row "stages" that ping-pong so the tensor core always has
 // one stage's MMA to run while the other stage's softmax is in flight.
 //
-//   warp 13      loader   : TMA (cp.async.bulk.tensor, 128B swizzle) Q stages + K/V ring
-//   warp 12      mma      : one thread issues tcgen05.mma; S = Q K^T (smem x smem) into TMEM,
+//   warps 0-3    stage 0 } softmax: tcgen05.ld one S row per thread -> mask, row max, exp2, row sum ->
+//   warps 4-7    stage 1 }   bf16/fp16 P written back over S in TMEM (tcgen05.st); O in TMEM is rescaled
+//                            only when the row max grew by more than 2^8. At the end of a tile the same
+//                            warps run the stage's epilogue: O / l -> 16-bit -> swizzled smem -> TMA store
+//                            (predicated stores on ragged packed tiles), LSE = (m + log2 l) ln 2.
+//   warp 8       mma      : one thread issues tcgen05.mma; S = Q K^T (smem x smem) into TMEM,
 //                           O += P V (P read from TMEM, V from smem as an MN-major operand)
-//   warps 0-3    softmax of stage 0: tcgen05.ld S row -> mask, row max, exp2, row sum ->
-//   warps 4-7    softmax of stage 1: bf16/fp16 P written back over S in TMEM (tcgen05.st);
-//                           rescales O in TMEM only when the row max grew by more than 2^8
-//   warps 8-11   epilogue : O / l -> 16-bit -> swizzled smem -> TMA store (or predicated
-//                           stores on ragged packed tiles), LSE = (m + log2 l) ln 2
+//   warp 9       loader   : TMA (cp.async.bulk.tensor, 128B swizzle) Q stages + K/V ring
+//
+// The Q stage buffers are released by the MMA thread as soon as the tile's last Q K^T has been read,
+// and the output is staged in its own smem tiles, so the next tile's Q load and first Q K^T overlap
+// the epilogue of the current tile.
 //
 // Replaces the reference kernels flash_attn_fwd / varlen_fwd
 // (flash-attn2-rs/src/device/forward/dense.rs:472-590, forward/mod.rs:1162-1407,
@@ -27,24 +31,25 @@ namespace {
 
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
-constexpr int kThreads = 512;
-constexpr int kSoftmaxRegs = 192;
-constexpr int kEpilogueRegs = 64;
-constexpr int kOtherRegs = 64;
+constexpr int kThreads = 384;   // 8 softmax warps + one warpgroup holding the MMA and the loader warp
+constexpr int kMmaWarp = 8;
+constexpr int kLoadWarp = 9;
+constexpr int kSoftmaxRegs = 200;
+constexpr int kOtherRegs = 104;
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain
 
 template <int D>
 struct FwdCfg {
   static constexpr int kAtoms = D / 64;                    // 128-byte swizzle atoms along D
   static constexpr int kTileBytes = kBlockN * D * 2;       // one Q stage / K / V tile
-  static constexpr int kSlots = (D == 128) ? 4 : 6;        // K/V ring depth
+  static constexpr int kSlots = (D == 128) ? 3 : 6;        // K/V ring depth
   static constexpr int kQOff = 0;
   static constexpr int kKVOff = 2 * kTileBytes;
-  static constexpr int kBarOff = kKVOff + kSlots * kTileBytes;
-  static constexpr int kNumBars = 2 * kSlots + 16;
+  static constexpr int kOOff = kKVOff + kSlots * kTileBytes;  // O staging for the TMA stores, one tile per stage
+  static constexpr int kBarOff = kOOff + 2 * kTileBytes;
+  static constexpr int kNumBars = 2 * kSlots + 18;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;  // tmem slot, abort flag
-  static constexpr int kStatOff = kMiscOff + 32;           // l and m exchange: [2 stages][128][2]
-  static constexpr int kSmemBytes = kStatOff + 2 * 128 * 2 * 4 + 1024;  // + alignment slack
+  static constexpr int kSmemBytes = kMiscOff + 32;  // the dynamic window must start 1024-aligned
   static constexpr uint32_t kTmemS0 = 0, kTmemS1 = 128, kTmemO0 = 256, kTmemO1 = 256 + D;
 };
 
@@ -123,24 +128,28 @@ __device__ __forceinline__ float tanh_approx(float x) {
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
   using Cfg = FwdCfg<D>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0u) {
+    // 128-byte swizzled tiles need a 1024-byte aligned base; report instead of computing garbage.
+    if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, kWaitNone + 1);
+    return;
+  }
   uint8_t* s_q = smem + Cfg::kQOff;
   uint8_t* s_kv = smem + Cfg::kKVOff;
+  uint8_t* s_o = smem + Cfg::kOOff;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOff);
   uint64_t* kv_full = bars;
   uint64_t* kv_empty = bars + Cfg::kSlots;
-  uint64_t* q_full = bars + 2 * Cfg::kSlots;  // [2]
+  uint64_t* q_full = bars + 2 * Cfg::kSlots;  // every array below is [2], one per stage
   uint64_t* q_empty = q_full + 2;
   uint64_t* s_full = q_full + 4;
   uint64_t* p_full = q_full + 6;
   uint64_t* pv_done = q_full + 8;
-  uint64_t* sm_final = q_full + 10;
-  uint64_t* o_free = q_full + 12;
-  uint64_t* epi_full = q_full + 14;
+  uint64_t* o_free = q_full + 10;        // O_s has been read out of TMEM
+  uint64_t* epi_full = q_full + 12;      // all 128 rows of O_s are staged in smem
+  uint64_t* o_stage_free = q_full + 14;  // the previous TMA store of stage s has read its staging tile
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::kMiscOff + 8);
-  float* s_stat = reinterpret_cast<float*>(smem + Cfg::kStatOff);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -159,17 +168,17 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
       mbar_init(&s_full[s], 1);
       mbar_init(&p_full[s], kBlockM);
       mbar_init(&pv_done[s], 1);
-      mbar_init(&sm_final[s], kBlockM);
       mbar_init(&o_free[s], kBlockM);
       mbar_init(&epi_full[s], kBlockM);
+      mbar_init(&o_stage_free[s], 1);
     }
     mbar_fence_init();
   }
-  if (warp == 12) {
+  if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  if (warp == 13 && lane == 0) {
+  if (warp == kLoadWarp && lane == 0) {
     tma_prefetch_desc(&p.tm_q);
     tma_prefetch_desc(&p.tm_k);
     tma_prefetch_desc(&p.tm_v);
@@ -181,19 +190,21 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   const uint32_t tmem = *tmem_slot;
 
   if (warp < 8) {
-    // ------------------------------------------------------------------ softmax
+    // ------------------------------------------------------------------ softmax + epilogue of stage s
     reg_alloc<kSoftmaxRegs>();
     const int s = warp >> 2;
     const int row_in = tid & 127;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_s = tmem + lane_addr + (s == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1);
     const uint32_t t_o = tmem + lane_addr + (s == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
+    uint8_t* stage_smem = s_o + s * Cfg::kTileBytes;
     const bool fancy = (p.softcap > 0.f) || (p.alibi != nullptr) || (p.scale_log2 < 0.f);
-    uint32_t n_sfull = 0, n_pv = 0, n_tile = 0;
+    uint32_t n_sfull = 0, n_pv = 0, n_store = 0;
     for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
       const Tile ti = get_tile(p, t);
       if (!ti.valid) continue;
-      const int row = ti.m0 + s * kBlockM + row_in;
+      const int r_lo = ti.m0 + s * kBlockM;
+      const int row = r_lo + row_in;
       const int nb_s = s ? ti.nb[1] : ti.nb[0];
       const int ne_s = s ? ti.ne[1] : ti.ne[0];
       float m = -INFINITY, l = 0.f;
@@ -228,7 +239,6 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           cs = 1.f;
         }
         // Mask only tiles that touch a boundary (warp-uniform test on the stage's row range).
-        const int r_lo = ti.m0 + s * kBlockM;
         const int r_hi = r_lo + kBlockM - 1;
         bool need_mask = (col0 + kBlockN > ti.sk);
         if (p.window_right >= 0) need_mask |= (col0 + kBlockN - 1 > r_lo + ti.off + p.window_right);
@@ -301,115 +311,86 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         ++n_pv;
       }
       if (!ok) break;
-      // Hand the row statistics to the epilogue once it is done with the previous tile.
-      if (!mbar_wait(&o_free[s], (n_tile & 1) ^ 1, ctl, kWaitSoftmaxPvDone)) break;
-      s_stat[(s * kBlockM + row_in) * 2] = l;
-      s_stat[(s * kBlockM + row_in) * 2 + 1] = m;
-      mbar_arrive(&sm_final[s]);
-      ++n_tile;
-    }
-  } else if (warp < 12) {
-    // ------------------------------------------------------------------ epilogue
-    reg_dealloc<kEpilogueRegs>();
-    const int row_in = tid & 127;
-    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    uint32_t n_tile = 0;
-    uint32_t n_pv[2] = {0, 0};
-    uint32_t n_epi[2] = {0, 0};
-    bool ok = true;
-    for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
-      const Tile ti = get_tile(p, t);
-      if (!ti.valid) continue;
-#pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        const int r_lo = ti.m0 + s * kBlockM;
-        const int row = r_lo + row_in;
-        const int iters = ti.ne[s] - ti.nb[s];
-        if (!mbar_wait(&sm_final[s], n_tile & 1, ctl, kWaitEpiFinal)) { ok = false; break; }
-        const float l = s_stat[(s * kBlockM + row_in) * 2];
-        const float m = s_stat[(s * kBlockM + row_in) * 2 + 1];
-        const bool tma_store = (p.cu_q == nullptr) || (r_lo + kBlockM <= ti.sq);
-        uint8_t* stage_smem = s_q + s * Cfg::kTileBytes;
-        if (iters > 0) {
-          n_pv[s] += iters;
-          if (!mbar_wait(&pv_done[s], (n_pv[s] - 1) & 1, ctl, kWaitEpiPvDone)) { ok = false; break; }
-          tc_fence_after();
-          const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-          const uint32_t t_o = tmem + lane_addr + (s == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t orr[32];
-            tmem_ld32(t_o + c * 32, orr);
-            tmem_wait_ld();
-            uint32_t w[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              w[i] = pack2<BF16>(__uint_as_float(orr[2 * i]) * inv_l, __uint_as_float(orr[2 * i + 1]) * inv_l);
-            if (tma_store) {
-              // 32 columns = 64 bytes = four 16-byte chunks of the row's 128-byte swizzle line.
-              uint8_t* rowp = stage_smem + (c / 2) * (kBlockM * 128) + row_in * 128;
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const int chunk = (c & 1) * 4 + q;
-                *reinterpret_cast<uint4*>(rowp + ((chunk ^ (row_in & 7)) << 4)) =
-                    make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
-              }
-            } else if (row < ti.sq) {
-              uint16_t* dst = reinterpret_cast<uint16_t*>(p.o_ptr) + ti.bq * p.o_batch_stride +
-                              static_cast<int64_t>(ti.q_row0 + row) * p.o_row_stride + ti.h * p.o_head_stride + c * 32;
-#pragma unroll
-              for (int q = 0; q < 4; ++q)
-                *reinterpret_cast<uint4*>(dst + q * 8) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
-            }
+      // ---- epilogue of this stage: O / l -> 16-bit -> swizzled smem -> one TMA store.
+      // A ragged tile of a packed batch (rows of the next sequence follow) uses predicated stores.
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o_ptr) + ti.bq * p.o_batch_stride +
+                       static_cast<int64_t>(ti.q_row0 + row) * p.o_row_stride + ti.h * p.o_head_stride;
+      const bool tma_store = (p.cu_q == nullptr) || (r_lo + kBlockM <= ti.sq);
+      if (ne_s > nb_s) {
+        if (tma_store) {
+          if (row_in == 0) {
+            tma_wait_group_read<0>();  // the store of the previous tile has read the staging tile
+            mbar_arrive(&o_stage_free[s]);
           }
-        } else if (row < ti.sq) {
-          // No key is visible to this stage: O = 0.
-          uint16_t* dst = reinterpret_cast<uint16_t*>(p.o_ptr) + ti.bq * p.o_batch_stride +
-                          static_cast<int64_t>(ti.q_row0 + row) * p.o_row_stride + ti.h * p.o_head_stride;
-#pragma unroll
-          for (int q = 0; q < D / 8; ++q) *reinterpret_cast<uint4*>(dst + q * 8) = make_uint4(0, 0, 0, 0);
+          if (!mbar_wait(&o_stage_free[s], n_store & 1, ctl, kWaitEpiFinal)) break;
         }
+        if (!mbar_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitEpiPvDone)) break;
+        tc_fence_after();
+        uint32_t orr[D];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tmem_ld32(t_o + c * 32, orr + c * 32);
+        tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(&o_free[s]);
-        if (row < ti.sq) {
-          const float lse = (l > 0.f) ? (m + lg2(l)) * 0.6931471805599453f : INFINITY;
-          p.lse_ptr[ti.bq * p.lse_batch_stride + ti.h * p.lse_head_stride + ti.q_row0 + row] = lse;
+        const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) {  // 16-byte chunks of the row
+          uint4 w;
+          w.x = pack2<BF16>(__uint_as_float(orr[8 * c]) * inv_l, __uint_as_float(orr[8 * c + 1]) * inv_l);
+          w.y = pack2<BF16>(__uint_as_float(orr[8 * c + 2]) * inv_l, __uint_as_float(orr[8 * c + 3]) * inv_l);
+          w.z = pack2<BF16>(__uint_as_float(orr[8 * c + 4]) * inv_l, __uint_as_float(orr[8 * c + 5]) * inv_l);
+          w.w = pack2<BF16>(__uint_as_float(orr[8 * c + 6]) * inv_l, __uint_as_float(orr[8 * c + 7]) * inv_l);
+          if (tma_store) {
+            // chunk c lives in swizzle atom c / 8, at position (c % 8) ^ (row % 8) of the row's 128-byte line
+            *reinterpret_cast<uint4*>(stage_smem + (c / 8) * (kBlockM * 128) + row_in * 128 +
+                                      (((c & 7) ^ (row_in & 7)) << 4)) = w;
+          } else if (row < ti.sq) {
+            *reinterpret_cast<uint4*>(orow + c * 8) = w;
+          }
         }
-        if (iters > 0 && tma_store) {
-          // All 128 rows staged -> one thread stores the tile.
+        if (tma_store) {
           fence_proxy_async_smem();
           mbar_arrive(&epi_full[s]);
           if (row_in == 0) {
-            if (!mbar_wait(&epi_full[s], n_epi[s] & 1, ctl, kWaitEpiFinal)) { ok = false; break; }
+            if (!mbar_wait(&epi_full[s], n_store & 1, ctl, kWaitEpiFinal)) break;
 #pragma unroll
             for (int a = 0; a < Cfg::kAtoms; ++a)
               tma_store_4d(&p.tm_o, stage_smem + a * (kBlockM * 128), a * 64, ti.h, ti.q_row0 + r_lo, ti.bq);
             tma_commit_group();
-            tma_wait_group_read<0>();
           }
-          ++n_epi[s];
+          ++n_store;
         }
-        if (row_in == 0) mbar_arrive(&q_empty[s]);
+      } else {
+        mbar_arrive(&o_free[s]);
+        if (row < ti.sq) {
+          // No key is visible to this stage: O = 0.
+#pragma unroll
+          for (int q = 0; q < D / 8; ++q) *reinterpret_cast<uint4*>(orow + q * 8) = make_uint4(0, 0, 0, 0);
+        }
       }
-      ++n_tile;
+      if (row < ti.sq) {
+        const float lse = (l > 0.f) ? (m + lg2(l)) * 0.6931471805599453f : INFINITY;
+        p.lse_ptr[ti.bq * p.lse_batch_stride + ti.h * p.lse_head_stride + ti.q_row0 + row] = lse;
+      }
     }
     if (row_in == 0) tma_wait_group<0>();
   } else {
     reg_dealloc<kOtherRegs>();
-    if (warp == 13 && lane == 0) {
+    if (warp == kLoadWarp && lane == 0) {
       // ---------------------------------------------------------------- loader
-      uint32_t n_tile = 0, kv_it = 0;
+      uint32_t slot = 0, ring_phase = 0, n_q0 = 0, n_q1 = 0;
       bool ok = true;
       auto load_kv = [&](const CUtensorMap* tm, int row, int head, int bcoord) -> bool {
-        const uint32_t slot = kv_it % Cfg::kSlots;
-        const uint32_t ph = (kv_it / Cfg::kSlots) & 1;
-        if (!mbar_wait(&kv_empty[slot], ph ^ 1, ctl, kWaitLoadKVEmpty)) return false;
+        if (!mbar_wait(&kv_empty[slot], ring_phase ^ 1, ctl, kWaitLoadKVEmpty)) return false;
         mbar_expect_tx(&kv_full[slot], Cfg::kTileBytes);
         uint8_t* dst = s_kv + slot * Cfg::kTileBytes;
 #pragma unroll
         for (int a = 0; a < Cfg::kAtoms; ++a)
           tma_load_4d(dst + a * (kBlockN * 128), tm, &kv_full[slot], a * 64, head, row, bcoord);
-        ++kv_it;
+        if (++slot == Cfg::kSlots) {
+          slot = 0;
+          ring_phase ^= 1;
+        }
         return true;
       };
       for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
@@ -417,7 +398,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         if (!ti.valid) continue;
         auto load_q = [&](int s) -> bool {
           if (ti.ne[s] <= ti.nb[s]) return true;
-          if (!mbar_wait(&q_empty[s], (n_tile & 1) ^ 1, ctl, kWaitLoadQEmpty)) return false;
+          uint32_t& nq = s ? n_q1 : n_q0;
+          if (!mbar_wait(&q_empty[s], (nq & 1) ^ 1, ctl, kWaitLoadQEmpty)) return false;
+          ++nq;
           mbar_expect_tx(&q_full[s], Cfg::kTileBytes);
 #pragma unroll
           for (int a = 0; a < Cfg::kAtoms; ++a)
@@ -432,7 +415,6 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           if (ok) ok = load_kv(&p.tm_v, ti.k_row0 + j * kBlockN, ti.hk, ti.bq);
         }
         if (ti.jlo >= ti.jhi && ok) ok = load_q(1);
-        ++n_tile;
       }
       if (!ok) {
         // Give copies that are still in flight time to land before the CTA exits.
@@ -440,79 +422,99 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         while (clock64() - t0 < 2000000) {
         }
       }
-    } else if (warp == 12 && lane == 0) {
+    } else if (warp == kMmaWarp && lane == 0) {
       // ---------------------------------------------------------------- mma issuer
-      const uint32_t idesc_qk = make_idesc(BF16, kBlockM, kBlockN, false, false);
-      const uint32_t idesc_pv = make_idesc(BF16, kBlockM, D, false, true);
-      const uint32_t q_addr = smem_u32(s_q);
-      const uint32_t kv_addr = smem_u32(s_kv);
-      uint32_t n_tile = 0, kv_it = 0;
-      uint32_t n_p[2] = {0, 0};
-      uint32_t n_q[2] = {0, 0};  // Q loads seen per stage (a stage without work loads nothing)
+      // Descriptors are built once; inside the loops an operand address is one 64-bit add of a
+      // compile-time constant (descriptor address field is in 16-byte units), so that the single
+      // issuing thread keeps the tensor pipe fed.
+      constexpr uint32_t idesc_qk = (1u << 4) | ((BF16 ? 1u : 0u) << 7) | ((BF16 ? 1u : 0u) << 10) |
+                                    (static_cast<uint32_t>(kBlockN >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
+      constexpr uint32_t idesc_pv = (1u << 4) | ((BF16 ? 1u : 0u) << 7) | ((BF16 ? 1u : 0u) << 10) | (1u << 16) |
+                                    (static_cast<uint32_t>(D >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
+      constexpr uint32_t kTile16 = Cfg::kTileBytes >> 4;
+      const uint64_t q_desc = make_smem_desc(smem_u32(s_q), 16, 1024);                 // K-major A
+      const uint64_t k_desc = make_smem_desc(smem_u32(s_kv), 16, 1024);                // K-major B
+      const uint64_t v_desc = make_smem_desc(smem_u32(s_kv), kBlockN * 128, 1024);     // MN-major B
+      uint32_t n_tile = 0;
+      uint32_t slot = 0, ring_phase = 0;  // K/V ring position of the next tile to consume
+      uint32_t n_p0 = 0, n_p1 = 0, n_q0 = 0, n_q1 = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
         const Tile ti = get_tile(p, t);
         if (!ti.valid) continue;
-        bool q_ready[2] = {false, false};
+        const int nb0 = ti.nb[0], ne0 = ti.ne[0], nb1 = ti.nb[1], ne1 = ti.ne[1];
+        bool q0_ready = false, q1_ready = false;
         // S_s = Q_s K^T over D in steps of 16 (32 bytes inside the 128-byte swizzle atom).
-        auto issue_qk = [&](int s, uint32_t k_base) -> bool {
-          if (!q_ready[s]) {
-            if (!mbar_wait(&q_full[s], n_q[s] & 1, ctl, kWaitMmaQFull)) return false;
-            ++n_q[s];
-            q_ready[s] = true;
+        auto issue_qk = [&](const int s, const uint32_t k_slot, const bool last) -> bool {
+          bool& ready = s ? q1_ready : q0_ready;
+          if (!ready) {
+            uint32_t& nq = s ? n_q1 : n_q0;
+            if (!mbar_wait(&q_full[s], nq & 1, ctl, kWaitMmaQFull)) return false;
+            ++nq;
+            ready = true;
           }
           tc_fence_after();
-          const uint32_t a_base = q_addr + s * Cfg::kTileBytes;
+          const uint64_t a = q_desc + s * kTile16;
+          const uint64_t b = k_desc + k_slot * kTile16;
           const uint32_t d_tmem = tmem + (s == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1);
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t o = (ks / 4) * (kBlockM * 128) + (ks % 4) * 32;
-            mma_ss(d_tmem, make_smem_desc(a_base + o, 16, 1024), make_smem_desc(k_base + o, 16, 1024), idesc_qk,
-                   ks > 0);
+            constexpr uint32_t kAtom16 = (kBlockM * 128) >> 4;
+            const uint32_t o = (ks / 4) * kAtom16 + (ks % 4) * 2;
+            mma_ss(d_tmem, a + o, b + o, idesc_qk, ks > 0 ? 1u : 0u);
           }
           mma_commit(&s_full[s]);
+          if (last) mma_commit(&q_empty[s]);  // the Q stage may be refilled for the next tile
           return true;
         };
         // O_s (+)= P_s V over the 128 keys in steps of 16 (P: 8 TMEM columns, V: 16 rows of 128 bytes).
-        auto issue_pv = [&](int s, uint32_t v_base, bool first) -> bool {
-          if (!mbar_wait(&p_full[s], n_p[s] & 1, ctl, kWaitMmaPFull)) return false;
-          ++n_p[s];
+        auto issue_pv = [&](const int s, const uint32_t v_slot, const bool first) -> bool {
+          uint32_t& np = s ? n_p1 : n_p0;
+          if (!mbar_wait(&p_full[s], np & 1, ctl, kWaitMmaPFull)) return false;
+          ++np;
           if (first && !mbar_wait(&o_free[s], (n_tile & 1) ^ 1, ctl, kWaitMmaOFree)) return false;
           tc_fence_after();
           const uint32_t d_tmem = tmem + (s == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
           const uint32_t a_tmem = tmem + (s == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1);
+          const uint64_t b = v_desc + v_slot * kTile16;
+          mma_ts(d_tmem, a_tmem, b, idesc_pv, first ? 0u : 1u);
 #pragma unroll
-          for (int ks = 0; ks < kBlockN / 16; ++ks)
-            mma_ts(d_tmem, a_tmem + ks * 8, make_smem_desc(v_base + ks * 2048, kBlockN * 128, 1024), idesc_pv,
-                   (!first) || ks > 0);
+          for (int ks = 1; ks < kBlockN / 16; ++ks) mma_ts(d_tmem, a_tmem + ks * 8, b + ks * (2048 >> 4), idesc_pv, 1u);
           mma_commit(&pv_done[s]);
           return true;
         };
-        auto wait_kv = [&](uint32_t it) -> bool {
-          return mbar_wait(&kv_full[it % Cfg::kSlots], (it / Cfg::kSlots) & 1, ctl, kWaitMmaKVFull);
+        auto advance = [&]() {
+          if (++slot == Cfg::kSlots) {
+            slot = 0;
+            ring_phase ^= 1;
+          }
         };
-        auto slot_addr = [&](uint32_t it) -> uint32_t { return kv_addr + (it % Cfg::kSlots) * Cfg::kTileBytes; };
-        auto act = [&](int s, int j) -> bool { return j >= ti.nb[s] && j < ti.ne[s]; };
 
         if (ti.jlo < ti.jhi) {
           // Ring order is K(jlo), V(jlo), K(jlo+1), V(jlo+1), ...
-          ok = wait_kv(kv_it);
-          if (ok && act(0, ti.jlo)) ok = issue_qk(0, slot_addr(kv_it));
-          if (ok && act(1, ti.jlo)) ok = issue_qk(1, slot_addr(kv_it));
-          if (ok) mma_commit(&kv_empty[kv_it % Cfg::kSlots]);
-          ++kv_it;
+          ok = mbar_wait(&kv_full[slot], ring_phase, ctl, kWaitMmaKVFull);
+          if (ok && ti.jlo >= nb0 && ti.jlo < ne0) ok = issue_qk(0, slot, ti.jlo == ne0 - 1);
+          if (ok && ti.jlo >= nb1 && ti.jlo < ne1) ok = issue_qk(1, slot, ti.jlo == ne1 - 1);
+          if (ok) mma_commit(&kv_empty[slot]);
+          advance();
           for (int j = ti.jlo; j < ti.jhi && ok; ++j) {
-            const uint32_t it_v = kv_it, it_k = kv_it + 1;
+            const uint32_t v_slot = slot, v_phase = ring_phase;
+            advance();
+            const uint32_t k_slot = slot, k_phase = ring_phase;
             const bool has_next = (j + 1 < ti.jhi);
-            ok = wait_kv(it_v);
-            if (ok && act(0, j)) ok = issue_pv(0, slot_addr(it_v), j == ti.nb[0]);
-            if (ok && has_next) ok = wait_kv(it_k);
-            if (ok && has_next && act(0, j + 1)) ok = issue_qk(0, slot_addr(it_k));
-            if (ok && act(1, j)) ok = issue_pv(1, slot_addr(it_v), j == ti.nb[1]);
-            if (ok) mma_commit(&kv_empty[it_v % Cfg::kSlots]);
-            if (ok && has_next && act(1, j + 1)) ok = issue_qk(1, slot_addr(it_k));
-            if (ok && has_next) mma_commit(&kv_empty[it_k % Cfg::kSlots]);
-            kv_it += has_next ? 2 : 1;
+            const bool a0 = j >= nb0 && j < ne0, a1 = j >= nb1 && j < ne1;
+            const bool n0 = has_next && j + 1 >= nb0 && j + 1 < ne0, n1 = has_next && j + 1 >= nb1 && j + 1 < ne1;
+            ok = mbar_wait(&kv_full[v_slot], v_phase, ctl, kWaitMmaKVFull);
+            if (ok && a0) ok = issue_pv(0, v_slot, j == nb0);
+            if (ok && has_next) ok = mbar_wait(&kv_full[k_slot], k_phase, ctl, kWaitMmaKVFull);
+            if (ok && n0) ok = issue_qk(0, k_slot, j + 1 == ne0 - 1);
+            if (ok && a1) ok = issue_pv(1, v_slot, j == nb1);
+            if (ok) mma_commit(&kv_empty[v_slot]);
+            if (ok && n1) ok = issue_qk(1, k_slot, j + 1 == ne1 - 1);
+            if (ok && has_next) {
+              mma_commit(&kv_empty[k_slot]);
+              advance();
+            }
           }
         }
         ++n_tile;
@@ -522,7 +524,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  if (warp == 12) tmem_dealloc(tmem, 512);
+  if (warp == kMmaWarp) tmem_dealloc(tmem, 512);
 }
 
 template <int D, bool BF16>
@@ -543,6 +545,7 @@ cudaError_t launch_one(const FwdParams& p, int num_sms, cudaStream_t stream) {
 }
 
 }  // namespace
+
 
 cudaError_t launch_fwd(const FwdParams& p, int head_dim, bool bf16, int num_sms, cudaStream_t stream) {
   if (p.num_tiles <= 0) return cudaSuccess;

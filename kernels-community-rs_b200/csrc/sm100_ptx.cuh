@@ -31,14 +31,17 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One try_wait. The last operand is the suspend-time hint in nanoseconds: the hardware may park the
+// thread until the phase completes (it is woken then) or the hint expires, so a polling warp does
+// not take issue slots from the warps that share its scheduler.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(0x989680u)
       : "memory");
   return ok != 0;
 }
@@ -60,10 +63,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   const long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 0u) {
-      if (*ctl.abort_flag) return false;
-      if (clock64() - t0 > FA2_WAIT_LIMIT_CYCLES) break;
-    }
+    if (*ctl.abort_flag) return false;
+    if ((it & 7u) == 0u && clock64() - t0 > FA2_WAIT_LIMIT_CYCLES) break;
   }
   if (!*ctl.abort_flag) {
     *ctl.abort_flag = 1;
