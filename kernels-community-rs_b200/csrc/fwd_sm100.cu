@@ -25,7 +25,23 @@
 #include "fa2_params.h"
 #include "fa2_launch.h"
 
+#ifndef FA2_POLY_PAIRS
+#define FA2_POLY_PAIRS 1
+#endif
+
 namespace fa2 {
+
+#ifdef FA2_TIMING
+// Debug build only: clock64 stamps of CTA 0 (never compiled into the shipped library).
+__device__ long long g_fwd_timing[1024];
+#define FA2_STAMP(slot) \
+  do { if (blockIdx.x == 0 && (slot) < 1024) g_fwd_timing[(slot)] = clock64(); } while (0)
+extern "C" __attribute__((visibility("default"))) int fa2_debug_fwd_timing(long long* out, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out, g_fwd_timing, sizeof(long long) * n));
+}
+#else
+#define FA2_STAMP(slot) do { } while (0)
+#endif
 
 namespace {
 
@@ -37,6 +53,7 @@ constexpr int kLoadWarp = 9;
 constexpr int kSoftmaxRegs = 200;
 constexpr int kOtherRegs = 104;
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain
+constexpr int kPolyPairs = FA2_POLY_PAIRS;    // of every 4 score pairs, how many take exp2 on the FMA pipe
 
 template <int D>
 struct FwdCfg {
@@ -212,66 +229,110 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
       if (p.alibi != nullptr) slope = p.alibi[ti.b * p.alibi_batch_stride + ti.h] * 1.4426950408889634f;
       bool ok = true;
       for (int j = nb_s; j < ne_s; ++j) {
+#ifdef FA2_TIMING
+        const bool tm_on = (row_in == 0) && n_sfull < 28;
+        const int tm_base = s * 256 + n_sfull * 8;
+        if (tm_on) FA2_STAMP(tm_base + 0);
+#endif
         if (!mbar_wait(&s_full[s], n_sfull & 1, ctl, kWaitSoftmaxSFull)) { ok = false; break; }
+#ifdef FA2_TIMING
+        if (tm_on) FA2_STAMP(tm_base + 1);
+#endif
         ++n_sfull;
         tc_fence_after();
+#if defined(FA2_EXP) && FA2_EXP == 3
+        { const long long tw = clock64(); while (clock64() - tw < 1500) { } }
+        tc_fence_before();
+        mbar_arrive(&p_full[s]);
+        ++n_pv;
+        continue;
+#endif
         uint32_t sr[kBlockN];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, sr + c * 32);
         tmem_wait_ld();
+#ifdef FA2_TIMING
+        if (tm_on) FA2_STAMP(tm_base + 2);
+#endif
         float cs = p.scale_log2;
         const int col0 = j * kBlockN;
-        if (fancy) {
-          // Scores leave this block already in the log2 domain.
-          const float inv_cap = (p.softcap > 0.f) ? p.scale / p.softcap : 0.f;
-          const float cap_l2 = p.softcap * 1.4426950408889634f;
-#pragma unroll
-          for (int i = 0; i < kBlockN; ++i) {
-            float x = __uint_as_float(sr[i]);
-            x = (p.softcap > 0.f) ? cap_l2 * tanh_approx(x * inv_cap) : x * p.scale_log2;
-            if (p.alibi != nullptr) {
-              const int col = col0 + i;
-              x += p.causal_alibi ? slope * static_cast<float>(col)
-                                  : -slope * fabsf(static_cast<float>(row + ti.off - col));
-            }
-            sr[i] = __float_as_uint(x);
-          }
-          cs = 1.f;
-        }
-        // Mask only tiles that touch a boundary (warp-uniform test on the stage's row range).
+        // Tiles that touch no mask boundary (warp-uniform test on the stage's row range) and need
+        // no score transform take the fast path.
         const int r_hi = r_lo + kBlockM - 1;
         bool need_mask = (col0 + kBlockN > ti.sk);
         if (p.window_right >= 0) need_mask |= (col0 + kBlockN - 1 > r_lo + ti.off + p.window_right);
         if (p.window_left >= 0) need_mask |= (col0 < r_hi + ti.off - p.window_left);
-        if (need_mask) {
-          int hi = ti.sk;
-          if (p.window_right >= 0) hi = min(hi, row + ti.off + p.window_right + 1);
-          int lo = 0;
-          if (p.window_left >= 0) lo = row + ti.off - p.window_left;
-          hi -= col0;
-          lo -= col0;
-#pragma unroll
-          for (int i = 0; i < kBlockN; ++i)
-            if (i < lo || i >= hi) sr[i] = __float_as_uint(-INFINITY);
-        }
-        float mx0 = __uint_as_float(sr[0]), mx1 = __uint_as_float(sr[1]);
-        float mx2 = __uint_as_float(sr[2]), mx3 = __uint_as_float(sr[3]);
-#pragma unroll
-        for (int i = 4; i < kBlockN; i += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(sr[i]));
-          mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
-        }
-        const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * cs;
-        const float m_new = fmaxf(m, m_tile);
-        // Keep the stale max unless it grew by more than 2^8: the final O / l is exact either way.
-        const bool grow = (m_new - m) > kRescaleThreshold;
+        bool grow;
         float alpha = 1.f;
-        if (grow) {
-          alpha = ex2(m - m_new);  // m = -inf gives 0
-          m = m_new;
-          l *= alpha;
+        if (!fancy && !need_mask) {
+          // ---- fast path: row max with 3-input max, then the O rescale decision
+          float mx0 = max3(__uint_as_float(sr[0]), __uint_as_float(sr[1]), __uint_as_float(sr[2]));
+          float mx1 = max3(__uint_as_float(sr[3]), __uint_as_float(sr[4]), __uint_as_float(sr[5]));
+          float mx2 = max3(__uint_as_float(sr[6]), __uint_as_float(sr[7]), __uint_as_float(sr[8]));
+          float mx3 = max3(__uint_as_float(sr[9]), __uint_as_float(sr[10]), __uint_as_float(sr[11]));
+#pragma unroll
+          for (int i = 12; i < kBlockN - 4; i += 8) {
+            mx0 = max3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+            mx1 = max3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+            mx2 = max3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
+            mx3 = max3(mx3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
+          }
+          mx0 = max3(mx0, __uint_as_float(sr[kBlockN - 4]), __uint_as_float(sr[kBlockN - 3]));
+          mx1 = max3(mx1, __uint_as_float(sr[kBlockN - 2]), __uint_as_float(sr[kBlockN - 1]));
+          const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2);
+          grow = (m_new - m) > kRescaleThreshold;
+          if (grow) {
+            alpha = ex2(m - m_new);
+            m = m_new;
+            l *= alpha;
+          }
+        } else {
+          if (fancy) {
+            // Scores leave this block already in the log2 domain.
+            const float inv_cap = (p.softcap > 0.f) ? p.scale / p.softcap : 0.f;
+            const float cap_l2 = p.softcap * 1.4426950408889634f;
+  #pragma unroll
+            for (int i = 0; i < kBlockN; ++i) {
+              float x = __uint_as_float(sr[i]);
+              x = (p.softcap > 0.f) ? cap_l2 * tanh_approx(x * inv_cap) : x * p.scale_log2;
+              if (p.alibi != nullptr) {
+                const int col = col0 + i;
+                x += p.causal_alibi ? slope * static_cast<float>(col)
+                                    : -slope * fabsf(static_cast<float>(row + ti.off - col));
+              }
+              sr[i] = __float_as_uint(x);
+            }
+            cs = 1.f;
+          }
+          if (need_mask) {
+            int hi = ti.sk;
+            if (p.window_right >= 0) hi = min(hi, row + ti.off + p.window_right + 1);
+            int lo = 0;
+            if (p.window_left >= 0) lo = row + ti.off - p.window_left;
+            hi -= col0;
+            lo -= col0;
+  #pragma unroll
+            for (int i = 0; i < kBlockN; ++i)
+              if (i < lo || i >= hi) sr[i] = __float_as_uint(-INFINITY);
+          }
+          float mx0 = __uint_as_float(sr[0]), mx1 = __uint_as_float(sr[1]);
+          float mx2 = __uint_as_float(sr[2]), mx3 = __uint_as_float(sr[3]);
+  #pragma unroll
+          for (int i = 4; i < kBlockN; i += 4) {
+            mx0 = fmaxf(mx0, __uint_as_float(sr[i]));
+            mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
+          }
+          const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * cs;
+          const float m_new = fmaxf(m, m_tile);
+          // Keep the stale max unless it grew by more than 2^8: the final O / l is exact either way.
+          grow = (m_new - m) > kRescaleThreshold;
+          if (grow) {
+            alpha = ex2(m - m_new);  // m = -inf gives 0
+            m = m_new;
+            l *= alpha;
+          }
         }
         if (j > nb_s && __any_sync(0xffffffffu, grow)) {
           // O of this stage is only touched by PV(j-1), which has to be complete.
@@ -287,27 +348,71 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             tmem_st16(t_o + c * 16, orr);
           }
         }
-        const float neg_m = (m == -INFINITY) ? 0.f : -m;
-        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#ifdef FA2_TIMING
+        if (tm_on) FA2_STAMP(tm_base + 3);
+#endif
+        if (!fancy && !need_mask) {
+          // ---- fast path: x = s * c - m with packed FMAs; kPolyPairs of every four pairs take their
+          // exponential on the FMA pipe, the others on the MUFU unit; packed row-sum accumulation.
+          const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2);
+          const uint64_t nm2 = pack_f32x2(-m, -m);  // m is finite here: the tile has no masked score
+          uint64_t acc0 = pack_f32x2(0.f, 0.f), acc1 = acc0;
 #pragma unroll
-        for (int i = 0; i < kBlockN; i += 4) {
-          const float p0 = ex2(fmaf(__uint_as_float(sr[i]), cs, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(sr[i + 1]), cs, neg_m));
-          const float p2 = ex2(fmaf(__uint_as_float(sr[i + 2]), cs, neg_m));
-          const float p3 = ex2(fmaf(__uint_as_float(sr[i + 3]), cs, neg_m));
-          l0 += p0;
-          l1 += p1;
-          l2 += p2;
-          l3 += p3;
-          sr[i / 2] = pack2<BF16>(p0, p1);
-          sr[i / 2 + 1] = pack2<BF16>(p2, p3);
+          for (int i = 0; i < kBlockN; i += 8) {
+            float x[8];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint64_t v = fma2(pack_f32x2(__uint_as_float(sr[i + 2 * q]), __uint_as_float(sr[i + 2 * q + 1])), c2, nm2);
+              unpack_f32x2(v, x[2 * q], x[2 * q + 1]);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (q >= 4 - kPolyPairs) {
+                exp2_poly2(x[2 * q], x[2 * q + 1]);
+              } else {
+                x[2 * q] = ex2(x[2 * q]);
+                x[2 * q + 1] = ex2(x[2 * q + 1]);
+              }
+            }
+            acc0 = add2(acc0, pack_f32x2(x[0], x[1]));
+            acc1 = add2(acc1, pack_f32x2(x[2], x[3]));
+            acc0 = add2(acc0, pack_f32x2(x[4], x[5]));
+            acc1 = add2(acc1, pack_f32x2(x[6], x[7]));
+#pragma unroll
+            for (int q = 0; q < 4; ++q) sr[i / 2 + q] = pack2<BF16>(x[2 * q], x[2 * q + 1]);
+          }
+          float a0, a1;
+          unpack_f32x2(add2(acc0, acc1), a0, a1);
+          l += a0 + a1;
+        } else {
+          const float neg_m = (m == -INFINITY) ? 0.f : -m;
+          float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+  #pragma unroll
+          for (int i = 0; i < kBlockN; i += 4) {
+            const float p0 = ex2(fmaf(__uint_as_float(sr[i]), cs, neg_m));
+            const float p1 = ex2(fmaf(__uint_as_float(sr[i + 1]), cs, neg_m));
+            const float p2 = ex2(fmaf(__uint_as_float(sr[i + 2]), cs, neg_m));
+            const float p3 = ex2(fmaf(__uint_as_float(sr[i + 3]), cs, neg_m));
+            l0 += p0;
+            l1 += p1;
+            l2 += p2;
+            l3 += p3;
+            sr[i / 2] = pack2<BF16>(p0, p1);
+            sr[i / 2 + 1] = pack2<BF16>(p2, p3);
+          }
+          l += (l0 + l1) + (l2 + l3);
         }
-        l += (l0 + l1) + (l2 + l3);
+#ifdef FA2_TIMING
+        if (tm_on) FA2_STAMP(tm_base + 4);
+#endif
         tmem_st32(t_s, sr);
         tmem_st32(t_s + 32, sr + 32);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&p_full[s]);
+#ifdef FA2_TIMING
+        if (tm_on) FA2_STAMP(tm_base + 5);
+#endif
         ++n_pv;
       }
       if (!ok) break;
@@ -463,6 +568,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             const uint32_t o = (ks / 4) * kAtom16 + (ks % 4) * 2;
             mma_ss(d_tmem, a + o, b + o, idesc_qk, ks > 0 ? 1u : 0u);
           }
+#ifdef FA2_TIMING
+          { const uint32_t np = s ? n_p1 : n_p0; if (np >= 1 && np <= 28) FA2_STAMP(512 + s * 128 + (np - 1) * 4 + 3); }
+#endif
           mma_commit(&s_full[s]);
           if (last) mma_commit(&q_empty[s]);  // the Q stage may be refilled for the next tile
           return true;
@@ -477,10 +585,19 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           const uint32_t d_tmem = tmem + (s == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
           const uint32_t a_tmem = tmem + (s == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1);
           const uint64_t b = v_desc + v_slot * kTile16;
+#ifdef FA2_TIMING
+          if (np <= 28) FA2_STAMP(512 + s * 128 + (np - 1) * 4 + 0);
+#endif
           mma_ts(d_tmem, a_tmem, b, idesc_pv, first ? 0u : 1u);
 #pragma unroll
           for (int ks = 1; ks < kBlockN / 16; ++ks) mma_ts(d_tmem, a_tmem + ks * 8, b + ks * (2048 >> 4), idesc_pv, 1u);
+#ifdef FA2_TIMING
+          if (np <= 28) FA2_STAMP(512 + s * 128 + (np - 1) * 4 + 1);
+#endif
           mma_commit(&pv_done[s]);
+#ifdef FA2_TIMING
+          if (np <= 28) FA2_STAMP(512 + s * 128 + (np - 1) * 4 + 2);
+#endif
           return true;
         };
         auto advance = [&]() {
