@@ -28,12 +28,24 @@
 
 namespace fa2 {
 
+#ifdef FA2_TIMING
+// Debug build only: clock64 stamps of CTA 0 (never compiled into the shipped library).
+__device__ long long g_bwd_timing[1024];
+#define FA2_BSTAMP(slot) \
+  do { if (blockIdx.x == 0 && (slot) < 1024) g_bwd_timing[(slot)] = clock64(); } while (0)
+extern "C" __attribute__((visibility("default"))) int fa2_debug_bwd_timing(long long* out, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out, g_bwd_timing, sizeof(long long) * n));
+}
+#else
+#define FA2_BSTAMP(slot) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int kBlk = 128;  // keys per CTA and query rows per iteration
 constexpr int kThreads = 512;
-constexpr int kComputeRegs = 176;
-constexpr int kDrainRegs = 104;
+constexpr int kComputeRegs = 152;
+constexpr int kDrainRegs = 152;
 constexpr int kMiscRegs = 56;
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -44,16 +56,15 @@ struct BwdCfg {
   static constexpr int kKOff = 0;
   static constexpr int kVOff = kTileBytes;
   static constexpr int kQOff = 2 * kTileBytes;     // 2 stages
-  static constexpr int kDOOff = 4 * kTileBytes;    // 1 stage
-  static constexpr int kDSOff = 5 * kTileBytes;    // [128 keys x 128 q] 16-bit
+  static constexpr int kDOOff = 4 * kTileBytes;    // 2 stages; a retired stage doubles as dQ staging
+  static constexpr int kDSOff = 6 * kTileBytes;    // [128 keys x 128 q] 16-bit
   static constexpr int kDSBytes = kBlk * kBlk * 2;
-  static constexpr int kStageOff = kDSOff + kDSBytes;  // dQ staging: [128 rows x 32 fp32]
-  static constexpr int kStageBytes = kBlk * 128;
-  static constexpr int kBarOff = kStageOff + kStageBytes;
-  static constexpr int kNumBars = 20;
+  static constexpr int kBarOff = kDSOff + kDSBytes;
+  static constexpr int kNumBars = 24;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kStatOff = kMiscOff + 32;       // lse / delta: [2 buffers][2][128] fp32
-  static constexpr int kSmemBytes = kStatOff + 2 * 2 * kBlk * 4 + 1024;
+  static constexpr int kSmemBytes = kStatOff + 2 * 2 * kBlk * 4;  // the dynamic window must start 1024-aligned
+  static constexpr int kPieceBytes = kBlk * 128;       // dQ staging piece: [128 rows x 32 fp32]
   static constexpr uint32_t kTmemDK = 0, kTmemDV = D, kTmemS = 256, kTmemDP = 384;
 };
 
@@ -66,11 +77,14 @@ struct KvTile {
 
 __device__ __forceinline__ KvTile get_kv_tile(const BwdParams& p, int t) {
   KvTile ti;
-  const int bh = p.batch * p.heads_k;
-  const int nblk = t / bh;
-  const int rem = t - nblk * bh;
-  ti.b = rem / p.heads_k;
-  ti.hk = rem - ti.b * p.heads_k;
+  // Consecutive CTAs walk the key blocks of one (batch, kv head): the head's Q, dO and its fp32
+  // dQ accumulator stay in L2 while the 16-odd CTAs that add into it run side by side. With a
+  // causal mask the first key blocks see the most query rows, so each head starts with its
+  // heaviest CTAs.
+  const int bh = t / p.num_nblk;
+  const int nblk = t - bh * p.num_nblk;
+  ti.b = bh / p.heads_k;
+  ti.hk = bh - ti.b * p.heads_k;
   ti.n0 = nblk * kBlk;
   if (p.cu_q != nullptr) {
     ti.q_row0 = p.cu_q[ti.b];
@@ -102,31 +116,33 @@ __device__ __forceinline__ KvTile get_kv_tile(const BwdParams& p, int t) {
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant__ BwdParams p) {
   using Cfg = BwdCfg<D>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0u) {
+    if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, kWaitNone + 1);
+    return;
+  }
   uint8_t* s_k = smem + Cfg::kKOff;
   uint8_t* s_v = smem + Cfg::kVOff;
   uint8_t* s_q = smem + Cfg::kQOff;
   uint8_t* s_do = smem + Cfg::kDOOff;
   uint8_t* s_ds = smem + Cfg::kDSOff;
-  uint8_t* s_stage = smem + Cfg::kStageOff;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOff);
   uint64_t* kv_full = bars + 0;
-  uint64_t* q_full = bars + 1;   // [2]
-  uint64_t* q_empty = bars + 3;  // [2]
-  uint64_t* do_full = bars + 5;
-  uint64_t* do_empty = bars + 6;
-  uint64_t* s_full = bars + 7;
-  uint64_t* p_full = bars + 8;
-  uint64_t* dp_full = bars + 9;
-  uint64_t* ds_full = bars + 10;
-  uint64_t* dq_full = bars + 11;
-  uint64_t* dq_free = bars + 12;
-  uint64_t* dkv_done = bars + 13;
-  uint64_t* stat_full = bars + 14;
-  uint64_t* stage_free = bars + 15;
-  uint64_t* stage_full = bars + 16;
-  uint64_t* epi_full = bars + 17;  // [2]
+  uint64_t* q_full = bars + 1;    // [2]
+  uint64_t* q_empty = bars + 3;   // [2]
+  uint64_t* do_full = bars + 5;   // [2]
+  uint64_t* do_empty = bars + 7;  // [2] dV has read the stage and the dQ drain is done staging in it
+  uint64_t* s_full = bars + 9;
+  uint64_t* p_full = bars + 10;
+  uint64_t* dp_full = bars + 11;
+  uint64_t* ds_full = bars + 12;
+  uint64_t* dq_full = bars + 13;
+  uint64_t* dq_free = bars + 14;
+  uint64_t* dkv_done = bars + 15;
+  uint64_t* stat_full = bars + 16;
+  uint64_t* stage_free = bars + 17;
+  uint64_t* stage_full = bars + 18;
+  uint64_t* epi_full = bars + 19;  // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::kMiscOff + 8);
   float* s_stat = reinterpret_cast<float*>(smem + Cfg::kStatOff);
@@ -146,8 +162,10 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       mbar_init(&q_full[s], 1);
       mbar_init(&q_empty[s], 1);
     }
-    mbar_init(do_full, 1);
-    mbar_init(do_empty, 1);
+    for (int st = 0; st < 2; ++st) {
+      mbar_init(&do_full[st], 1);
+      mbar_init(&do_empty[st], want_dq ? 2 : 1);
+    }
     mbar_init(s_full, 1);
     mbar_init(p_full, 256);
     mbar_init(dp_full, 1);
@@ -194,19 +212,21 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         const int hq = ti.hk * p.group + it / ti.n_m;
         const int m0 = (ti.m_start + it % ti.n_m) * kBlk;
         const int st = it & 1;
-        ok = mbar_wait(&q_empty[st], ((it >> 1) & 1) ^ 1, ctl, kWaitBwd + 1);
+        const uint32_t ph = (it >> 1) & 1;
+        ok = mbar_wait(&q_empty[st], ph ^ 1, ctl, kWaitBwd + 1);
         if (!ok) break;
         mbar_expect_tx(&q_full[st], Cfg::kTileBytes);
 #pragma unroll
         for (int a = 0; a < Cfg::kAtoms; ++a)
           tma_load_4d(s_q + st * Cfg::kTileBytes + a * (kBlk * 128), &p.tm_q, &q_full[st], a * 64, hq,
                       ti.q_row0 + m0, ti.bq);
-        ok = mbar_wait(do_empty, (it & 1) ^ 1, ctl, kWaitBwd + 2);
+        ok = mbar_wait(&do_empty[st], ph ^ 1, ctl, kWaitBwd + 2);
         if (!ok) break;
-        mbar_expect_tx(do_full, Cfg::kTileBytes);
+        mbar_expect_tx(&do_full[st], Cfg::kTileBytes);
 #pragma unroll
         for (int a = 0; a < Cfg::kAtoms; ++a)
-          tma_load_4d(s_do + a * (kBlk * 128), &p.tm_do, do_full, a * 64, hq, ti.q_row0 + m0, ti.bq);
+          tma_load_4d(s_do + st * Cfg::kTileBytes + a * (kBlk * 128), &p.tm_do, &do_full[st], a * 64, hq,
+                      ti.q_row0 + m0, ti.bq);
       }
       if (!ok) {
         const long long t0 = clock64();
@@ -215,82 +235,108 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       }
     } else if (warp == 1 && lane == 0) {
       // ---------------------------------------------------------------- mma issuer
-      const uint32_t idesc_qk = make_idesc(BF16, kBlk, kBlk, false, false);  // S^T, dP^T
-      const uint32_t idesc_dv = make_idesc(BF16, kBlk, D, false, true);      // dV (A in TMEM), dK
-      const uint32_t idesc_dq = make_idesc(BF16, kBlk, D, true, true);       // dQ
-      const uint32_t k_addr = smem_u32(s_k), v_addr = smem_u32(s_v), q_addr = smem_u32(s_q);
-      const uint32_t do_addr = smem_u32(s_do), ds_addr = smem_u32(s_ds);
-      auto kmajor_pair = [&](uint32_t d_tmem, uint32_t a_base, uint32_t b_base) {
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t o = (ks / 4) * (kBlk * 128) + (ks % 4) * 32;
-          mma_ss(d_tmem, make_smem_desc(a_base + o, 16, 1024), make_smem_desc(b_base + o, 16, 1024), idesc_qk, ks > 0);
-        }
+      // Descriptors are built once; in the loops an operand address is one 64-bit add of a constant
+      // (the descriptor's address field counts 16-byte units).
+      constexpr uint32_t kBase = (1u << 4) | ((BF16 ? 1u : 0u) << 7) | ((BF16 ? 1u : 0u) << 10) |
+                                 (static_cast<uint32_t>(kBlk >> 4) << 24);
+      constexpr uint32_t idesc_qk = kBase | (static_cast<uint32_t>(kBlk >> 3) << 17);             // S^T, dP^T
+      constexpr uint32_t idesc_dv = kBase | (static_cast<uint32_t>(D >> 3) << 17) | (1u << 16);   // dV, dK: B MN-major
+      constexpr uint32_t idesc_dq = idesc_dv | (1u << 15);                                        // dQ: A and B MN-major
+      constexpr uint32_t kTile16 = Cfg::kTileBytes >> 4;
+      constexpr uint32_t kAtom16 = (kBlk * 128) >> 4;
+      // One base descriptor (K-major view of the start of shared memory); every operand is that
+      // plus a constant: its byte offset / 16, and for the MN-major views the larger leading offset.
+      const uint64_t base = make_smem_desc(smem_u32(smem), 16, 1024);
+      constexpr uint64_t kMn = static_cast<uint64_t>(((kBlk * 128) >> 4) - 1) << 16;
+      const uint64_t k_kmaj = base + (Cfg::kKOff >> 4), k_mn = k_kmaj + kMn;
+      const uint64_t v_kmaj = base + (Cfg::kVOff >> 4);
+      const uint64_t q_kmaj = base + (Cfg::kQOff >> 4), q_mn = q_kmaj + kMn;
+      const uint64_t do_kmaj = base + (Cfg::kDOOff >> 4), do_mn = do_kmaj + kMn;
+      const uint64_t ds_kmaj = base + (Cfg::kDSOff >> 4), ds_mn = ds_kmaj + kMn;
+      // [keys x q] = A[keys x d] B[q x d]^T, both K-major, over d in steps of 16
+      auto kmajor_pair = [&](uint32_t d_tmem, uint64_t a, uint64_t b) {
+        static_for<D / 16>([&](auto ks) {
+          constexpr uint32_t o = (ks.value / 4) * kAtom16 + (ks.value % 4) * 2;
+          mma_ss_o<o, o>(d_tmem, a, b, idesc_qk, ks.value > 0 ? 1u : 0u);
+        });
       };
       bool ok = n_iter > 0;
       if (ok) ok = mbar_wait(kv_full, 0, ctl, kWaitBwd + 3);
       if (ok) ok = mbar_wait(&q_full[0], 0, ctl, kWaitBwd + 4);
       if (ok) {
         tc_fence_after();
-        kmajor_pair(tmem + Cfg::kTmemS, k_addr, q_addr);
+        kmajor_pair(tmem + Cfg::kTmemS, k_kmaj, q_kmaj);
         mma_commit(s_full);
-        ok = mbar_wait(do_full, 0, ctl, kWaitBwd + 5);
+        ok = mbar_wait(&do_full[0], 0, ctl, kWaitBwd + 5);
       }
       if (ok) {
         tc_fence_after();
-        kmajor_pair(tmem + Cfg::kTmemDP, v_addr, do_addr);
+        kmajor_pair(tmem + Cfg::kTmemDP, v_kmaj, do_kmaj);
         mma_commit(dp_full);
       }
       for (int it = 0; it < n_iter && ok; ++it) {
-        const int st = it & 1;
-        const uint32_t q_it = q_addr + st * Cfg::kTileBytes;
+        const uint32_t st = it & 1;
+        const uint32_t nph = ((it + 1) >> 1) & 1;  // phase of the stage barriers of iteration it + 1
         const bool has_next = it + 1 < n_iter;
+        const uint32_t acc = it > 0 ? 1u : 0u;
         // dV += P^T dO   (P^T: two 32-column halves at S + 0 and S + 64)
+        if (it < 20) FA2_BSTAMP(256 + it * 16 + 0);
         ok = mbar_wait(p_full, it & 1, ctl, kWaitBwd + 6);
         if (!ok) break;
+        if (it < 20) FA2_BSTAMP(256 + it * 16 + 1);
         tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < kBlk / 16; ++ks) {
-          const uint32_t a_tmem = tmem + Cfg::kTmemS + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8);
-          mma_ts(tmem + Cfg::kTmemDV, a_tmem, make_smem_desc(do_addr + ks * 2048, kBlk * 128, 1024), idesc_dv,
-                 it > 0 || ks > 0);
+        {
+          const uint64_t b = do_mn + st * kTile16;
+          static_for<kBlk / 16>([&](auto ks) {
+            mma_ts_o<(ks.value / 4) * 64 + (ks.value % 4) * 8, ks.value * (2048 >> 4)>(
+                tmem + Cfg::kTmemDV, tmem + Cfg::kTmemS, b, idesc_dv, ks.value > 0 ? 1u : acc);
+          });
         }
-        mma_commit(do_empty);
+        mma_commit(&do_empty[st]);
+        if (it < 20) FA2_BSTAMP(256 + it * 16 + 2);
         // dQ = dS K   (into the dP^T columns, which the compute warps have drained)
         ok = mbar_wait(ds_full, it & 1, ctl, kWaitBwd + 7);
         if (!ok) break;
+        if (it < 20) FA2_BSTAMP(256 + it * 16 + 3);
         tc_fence_after();
         if (want_dq) {
-#pragma unroll
-          for (int ks = 0; ks < kBlk / 16; ++ks)
-            mma_ss(tmem + Cfg::kTmemDP, make_smem_desc(ds_addr + ks * 2048, kBlk * 128, 1024),
-                   make_smem_desc(k_addr + ks * 2048, kBlk * 128, 1024), idesc_dq, ks > 0);
+          static_for<kBlk / 16>([&](auto ks) {
+            mma_ss_o<ks.value * (2048 >> 4), ks.value * (2048 >> 4)>(tmem + Cfg::kTmemDP, ds_mn, k_mn, idesc_dq,
+                                                                      ks.value > 0 ? 1u : 0u);
+          });
           mma_commit(dq_full);
         }
+        if (it < 20) FA2_BSTAMP(256 + it * 16 + 4);
         // S^T of the next iteration
         if (has_next) {
-          ok = mbar_wait(&q_full[st ^ 1], ((it + 1) >> 1) & 1, ctl, kWaitBwd + 8);
+          ok = mbar_wait(&q_full[st ^ 1], nph, ctl, kWaitBwd + 8);
           if (!ok) break;
           tc_fence_after();
-          kmajor_pair(tmem + Cfg::kTmemS, k_addr, q_addr + (st ^ 1) * Cfg::kTileBytes);
+          kmajor_pair(tmem + Cfg::kTmemS, k_kmaj, q_kmaj + (st ^ 1) * kTile16);
           mma_commit(s_full);
         }
+        if (it < 20) FA2_BSTAMP(256 + it * 16 + 5);
         // dK += dS^T Q
-#pragma unroll
-        for (int ks = 0; ks < kBlk / 16; ++ks) {
-          const uint32_t o = (ks / 4) * (kBlk * 128) + (ks % 4) * 32;
-          mma_ss(tmem + Cfg::kTmemDK, make_smem_desc(ds_addr + o, 16, 1024),
-                 make_smem_desc(q_it + ks * 2048, kBlk * 128, 1024), idesc_dv, it > 0 || ks > 0);
+        {
+          const uint64_t b = q_mn + st * kTile16;
+          static_for<kBlk / 16>([&](auto ks) {
+            mma_ss_o<(ks.value / 4) * kAtom16 + (ks.value % 4) * 2, ks.value * (2048 >> 4)>(
+                tmem + Cfg::kTmemDK, ds_kmaj, b, idesc_dv, ks.value > 0 ? 1u : acc);
+          });
         }
         mma_commit(&q_empty[st]);
+        if (it < 20) FA2_BSTAMP(256 + it * 16 + 6);
         // dP^T of the next iteration, once the dQ tile has left TMEM
         if (has_next) {
-          ok = mbar_wait(do_full, (it + 1) & 1, ctl, kWaitBwd + 9);
+          ok = mbar_wait(&do_full[st ^ 1], nph, ctl, kWaitBwd + 9);
+          if (it < 20) FA2_BSTAMP(256 + it * 16 + 7);
           if (ok && want_dq) ok = mbar_wait(dq_free, it & 1, ctl, kWaitBwd + 10);
           if (!ok) break;
+          if (it < 20) FA2_BSTAMP(256 + it * 16 + 8);
           tc_fence_after();
-          kmajor_pair(tmem + Cfg::kTmemDP, v_addr, do_addr);
+          kmajor_pair(tmem + Cfg::kTmemDP, v_kmaj, do_kmaj + (st ^ 1) * kTile16);
           mma_commit(dp_full);
+          if (it < 20) FA2_BSTAMP(256 + it * 16 + 9);
         }
       }
       if (ok) mma_commit(dkv_done);
@@ -326,13 +372,16 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         }
         stat[ct] = val;
       }
+      if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 0);
       mbar_arrive(stat_full);
       if (!mbar_wait(stat_full, it & 1, ctl, kWaitBwd + 15)) { ok = false; break; }
       const float4* lse4 = reinterpret_cast<const float4*>(stat + wg * 64);
       const float4* dl4 = reinterpret_cast<const float4*>(stat + kBlk + wg * 64);
 
       // ---- phase A: P^T = exp2(S^T c - lse)
+      if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 1);
       if (!mbar_wait(s_full, it & 1, ctl, kWaitBwd + 11)) { ok = false; break; }
+      if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 2);
       tc_fence_after();
       uint32_t sr[64];
       tmem_ld32(t_s, sr);
@@ -368,9 +417,11 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(p_full);
+      if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 3);
 
       // ---- phase B: dS^T = P^T (dP^T - delta)
       if (!mbar_wait(dp_full, it & 1, ctl, kWaitBwd + 12)) { ok = false; break; }
+      if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 4);
       tc_fence_after();
       tmem_ld32(t_dp, sr);
       tmem_ld32(t_dp + 32, sr + 32);
@@ -390,6 +441,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       }
       fence_proxy_async_smem();
       mbar_arrive(ds_full);
+      if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 5);
     }
     // ---- epilogue: warpgroup 0 writes dK (scaled), warpgroup 1 writes dV
     if (ok) {
@@ -447,52 +499,71 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------------ dQ drain
-    reg_dealloc<kDrainRegs>();
+    // The whole 128 x D fp32 tile goes to registers at once so that the dP^T / dQ columns are free
+    // for the next iteration right away; it then leaves through the dO stage this iteration has
+    // retired (two 16 KB pieces at a time) as cp.reduce.async.bulk adds into the accumulator.
+    reg_alloc<kDrainRegs>();
     const int rt = tid - 384;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_dq = tmem + lane_addr + Cfg::kTmemDP;
-    uint8_t* rowp = s_stage + rt * 128;
     if (want_dq) {
-      uint32_t n_piece = 0;
+      uint32_t n_round = 0;
       bool ok = true;
       for (int it = 0; it < n_iter && ok; ++it) {
         const int hq = ti.hk * p.group + it / ti.n_m;
         const int m0 = (ti.m_start + it % ti.n_m) * kBlk;
+        const uint32_t st = it & 1;
+        uint8_t* stage = s_do + st * Cfg::kTileBytes;
         if (!mbar_wait(dq_full, it & 1, ctl, kWaitBwd + 14)) break;
+        if (rt == 0 && it < 20) FA2_BSTAMP(640 + it * 4 + 0);
         tc_fence_after();
+        uint32_t acc[D];
 #pragma unroll
-        for (int half = 0; half < D / 64; ++half) {
-          uint32_t acc[64];
-          tmem_ld32(t_dq + half * 64, acc);
-          tmem_ld32(t_dq + half * 64 + 32, acc + 32);
-          tmem_wait_ld();
-          if (half == D / 64 - 1) {
-            tc_fence_before();
-            mbar_arrive(dq_free);
-          }
+        for (int c = 0; c < D / 32; ++c) tmem_ld32(t_dq + c * 32, acc + c * 32);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(dq_free);
+        if (rt == 0 && it < 20) FA2_BSTAMP(640 + it * 4 + 1);
+        constexpr int kRounds = (D / 32 + 1) / 2;                          // two pieces per round
+        constexpr int kPiecesPerRound = (Cfg::kTileBytes >= 2 * Cfg::kPieceBytes) ? 2 : 1;
 #pragma unroll
-          for (int piece = 0; piece < 2; ++piece) {
-            // The previous reduce must have finished reading the staging buffer.
+        for (int r = 0; r < D / 32 / kPiecesPerRound; ++r) {
+          if (r > 0) {
+            // The reduces of the previous round must have read the staging pieces.
             if (rt == 0) {
               tma_wait_group_read<0>();
               mbar_arrive(stage_free);
             }
-            if (!mbar_wait(stage_free, n_piece & 1, ctl, kWaitBwd + 17)) { ok = false; break; }
+            if (!mbar_wait(stage_free, n_round & 1, ctl, kWaitBwd + 17)) { ok = false; break; }
+            ++n_round;
+          }
+#pragma unroll
+          for (int pc = 0; pc < kPiecesPerRound; ++pc) {
+            uint8_t* rowp = stage + pc * Cfg::kPieceBytes + rt * 128;
+            const int c0 = (r * kPiecesPerRound + pc) * 32;
 #pragma unroll
             for (int c = 0; c < 8; ++c)
               *reinterpret_cast<uint4*>(rowp + ((c ^ (rt & 7)) << 4)) =
-                  make_uint4(acc[piece * 32 + 4 * c], acc[piece * 32 + 4 * c + 1], acc[piece * 32 + 4 * c + 2],
-                             acc[piece * 32 + 4 * c + 3]);
-            fence_proxy_async_smem();
-            mbar_arrive(stage_full);
-            if (rt == 0) {
-              if (!mbar_wait(stage_full, n_piece & 1, ctl, kWaitBwd + 18)) { ok = false; break; }
-              tma_reduce_add_4d(&p.tm_dqa, s_stage, half * 64 + piece * 32, hq, ti.q_row0 + m0, ti.bq);
-              tma_commit_group();
-            }
-            ++n_piece;
+                  make_uint4(acc[c0 + 4 * c], acc[c0 + 4 * c + 1], acc[c0 + 4 * c + 2], acc[c0 + 4 * c + 3]);
           }
-          if (!ok) break;
+          fence_proxy_async_smem();
+          mbar_arrive(stage_full);
+          if (rt == 0) {
+            if (!mbar_wait(stage_full, (it * (D / 32 / kPiecesPerRound) + r) & 1, ctl, kWaitBwd + 18)) { ok = false; break; }
+#pragma unroll
+            for (int pc = 0; pc < kPiecesPerRound; ++pc)
+              tma_reduce_add_4d(&p.tm_dqa, stage + pc * Cfg::kPieceBytes, (r * kPiecesPerRound + pc) * 32, hq,
+                                ti.q_row0 + m0, ti.bq);
+            tma_commit_group();
+          }
+        }
+        (void)kRounds;
+        if (!ok) break;
+        // Hand the stage back to the loader once the last reduces have read it.
+        if (rt == 0) {
+          tma_wait_group_read<0>();
+          mbar_arrive(&do_empty[st]);
+          if (it < 20) FA2_BSTAMP(640 + it * 4 + 2);
         }
       }
       if (rt == 0) tma_wait_group<0>();

@@ -26,7 +26,7 @@
 #include "fa2_launch.h"
 
 #ifndef FA2_POLY_PAIRS
-#define FA2_POLY_PAIRS 1
+#define FA2_POLY_PAIRS 0
 #endif
 
 namespace fa2 {

@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 #include <cuda.h>
 #include <stdint.h>
+#include <type_traits>
 
 namespace fa2 {
 
@@ -192,6 +193,38 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Variants that add compile-time offsets (in 16-byte units) to the descriptors inside the asm
+// block: an unrolled k-step loop then costs two adds per MMA and no registers for precomputed
+// descriptors (the compiler cannot hoist what it cannot see).
+template <uint32_t AOFF16, uint32_t BOFF16>
+__device__ __forceinline__ void mma_ss_o(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 ra, rb;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "add.s64 ra, %1, %5;\n\tadd.s64 rb, %2, %6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], ra, rb, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "n"(AOFF16), "n"(BOFF16)
+      : "memory");
+}
+template <uint32_t ACOL, uint32_t BOFF16>
+__device__ __forceinline__ void mma_ts_o(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 rb;\n\t.reg .b32 ta;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "add.s64 rb, %2, %6;\n\tadd.u32 ta, %1, %5;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], rb, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "n"(ACOL), "n"(BOFF16)
+      : "memory");
+}
+// Calls f(std::integral_constant<int, 0>{}) ... f(integral_constant<int, N-1>{}).
+template <int N, int I = 0, class F>
+__device__ __forceinline__ void static_for(F&& f) {
+  if constexpr (I < N) {
+    f(std::integral_constant<int, I>{});
+    static_for<N, I + 1>(f);
+  }
+}
+
 // Arrive once on `bar` when every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
