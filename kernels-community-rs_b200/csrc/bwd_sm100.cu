@@ -151,6 +151,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const WaitCtl ctl{abort_flag, p.status};
+  if (threadIdx.x == 0) FA2_BSTAMP(900);
   const KvTile ti = get_kv_tile(p, blockIdx.x);
   if (!ti.valid) return;
   const bool want_dq = (p.which & 1) != 0;
@@ -179,6 +180,25 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     mbar_init(&epi_full[0], kBlk);
     mbar_init(&epi_full[1], kBlk);
     mbar_fence_init();
+    // The first loads go out before the rest of the CTA is set up (TMEM allocation, the block-wide
+    // barrier): their latency is the longest item of a CTA's start.
+    if (ti.n_iter > 0) {
+      const int hq0 = ti.hk * p.group;
+      const int m00 = ti.m_start * kBlk;
+      mbar_expect_tx(kv_full, 2 * Cfg::kTileBytes);
+      mbar_expect_tx(&q_full[0], Cfg::kTileBytes);
+      mbar_expect_tx(&do_full[0], Cfg::kTileBytes);
+#pragma unroll
+      for (int a = 0; a < Cfg::kAtoms; ++a) {
+        tma_load_4d(s_k + a * (kBlk * 128), &p.tm_k, kv_full, a * 64, ti.hk, ti.k_row0 + ti.n0, ti.bq);
+        tma_load_4d(s_q + a * (kBlk * 128), &p.tm_q, &q_full[0], a * 64, hq0, ti.q_row0 + m00, ti.bq);
+      }
+#pragma unroll
+      for (int a = 0; a < Cfg::kAtoms; ++a) {
+        tma_load_4d(s_v + a * (kBlk * 128), &p.tm_v, kv_full, a * 64, ti.hk, ti.k_row0 + ti.n0, ti.bq);
+        tma_load_4d(s_do + a * (kBlk * 128), &p.tm_do, &do_full[0], a * 64, hq0, ti.q_row0 + m00, ti.bq);
+      }
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -196,19 +216,15 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const int n_iter = ti.n_iter;
+  if (threadIdx.x == 0) FA2_BSTAMP(901);
 
   if (warp < 4) {
     reg_dealloc<kMiscRegs>();
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------------- loader
-      if (n_iter > 0) mbar_expect_tx(kv_full, 2 * Cfg::kTileBytes);
-#pragma unroll
-      for (int a = 0; a < Cfg::kAtoms && n_iter > 0; ++a) {
-        tma_load_4d(s_k + a * (kBlk * 128), &p.tm_k, kv_full, a * 64, ti.hk, ti.k_row0 + ti.n0, ti.bq);
-        tma_load_4d(s_v + a * (kBlk * 128), &p.tm_v, kv_full, a * 64, ti.hk, ti.k_row0 + ti.n0, ti.bq);
-      }
+      // K, V and the first Q / dO tiles were requested during set-up.
       bool ok = true;
-      for (int it = 0; it < n_iter && ok; ++it) {
+      for (int it = 1; it < n_iter && ok; ++it) {
         const int hq = ti.hk * p.group + it / ti.n_m;
         const int m0 = (ti.m_start + it % ti.n_m) * kBlk;
         const int st = it & 1;
@@ -262,7 +278,9 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       };
       bool ok = n_iter > 0;
       if (ok) ok = mbar_wait(kv_full, 0, ctl, kWaitBwd + 3);
+      FA2_BSTAMP(902);
       if (ok) ok = mbar_wait(&q_full[0], 0, ctl, kWaitBwd + 4);
+      FA2_BSTAMP(903);
       if (ok) {
         tc_fence_after();
         kmajor_pair(tmem + Cfg::kTmemS, k_kmaj, q_kmaj);
@@ -340,6 +358,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         }
       }
       if (ok) mma_commit(dkv_done);
+      FA2_BSTAMP(904);
     }
   } else if (warp < 12) {
     // ------------------------------------------------------------------ compute
@@ -454,6 +473,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       uint8_t* stage = s_q + wg * Cfg::kTileBytes;
       bool done = true;
       if (n_iter > 0) done = mbar_wait(dkv_done, 0, ctl, kWaitBwd + 13);
+      if (ct == 0) FA2_BSTAMP(905);
       if (done && store) {
         tc_fence_after();
         uint16_t* grow = gptr + ti.bq * p.dkv_batch_stride + static_cast<int64_t>(ti.k_row0 + kpos) * p.dkv_row_stride +
@@ -572,6 +592,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   __syncwarp();
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) FA2_BSTAMP(906);
   if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
