@@ -124,6 +124,29 @@ typedef struct fa2_bwd_args {
 FA2_API int64_t fa2_bwd_workspace_bytes(const fa2_bwd_args* args);
 FA2_API int fa2_bwd(const fa2_bwd_args* args, void* stream);
 
+/* Backward that allocates nothing. No counterpart in the reference crate (its host layer always
+ * allocates its workspaces through the tvm-ffi environment allocator).
+ *
+ * For callers that may not call cudaMalloc at all - a serving loop whose device memory was
+ * partitioned up front, an embedding runtime that owns the device heap, a sandboxed plugin host -
+ * this variant of fa2_bwd keeps the fp32 dQ accumulator (and the kernels' status word) in device
+ * arrays that are part of the library image. It ignores args->dq_accum / dq_accum_bytes; the caller
+ * still passes every input and output. Neither this call nor anything it reaches calls cudaMalloc,
+ * cudaFree or an allocating library routine.
+ *
+ * Limits and rules:
+ *  - dense tensors only, which = 3, and batch * seqlen_q * heads * head_dim must not exceed
+ *    FA2_BWD_STATIC_MAX_ELEMENTS (4,194,304: a 16 MiB array that every GPU which loads the
+ *    library holds until the process exits); larger problems are rejected with FA2_E_VALUE;
+ *  - the first call on a device looks up the arrays' device addresses (cudaGetSymbolAddress, with
+ *    that device current). Make that first call outside any stream capture;
+ *  - all calls share the one accumulator: each call clears the part it uses, and two calls whose
+ *    GPU work overlaps (different streams, or different threads) race on it. Serialise them;
+ *  - the kernels' pipeline status of these calls lands in the library image too and is not what
+ *    fa2_device_status() reads (that call allocates on first use). */
+#define FA2_BWD_STATIC_MAX_ELEMENTS 4194304
+FA2_API int fa2_bwd_static(const fa2_bwd_args* args, void* stream);
+
 /* Message of the last failed call on this thread ("" if none). */
 FA2_API const char* fa2_last_error(void);
 

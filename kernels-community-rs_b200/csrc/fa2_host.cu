@@ -441,6 +441,152 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
   return FA2_OK;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Backward for callers that cannot allocate device memory.
+//
+// Some hosts of this library run where cudaMalloc is off limits: inside a real-time or
+// latency-critical serving loop whose memory was carved up front, under a framework that owns
+// every byte of the device heap, or in a sandbox where the allocation calls are simply not
+// permitted. fa2_bwd needs a caller-provided fp32 dQ accumulator, and this library's own set-up
+// allocates a status word; fa2_bwd_static needs neither. Its accumulator and its status word are
+// file-scope device arrays that live in the module image: every GPU that loads the library holds
+// them (16 MiB + 4 bytes) until the process exits.
+//
+// The array name below is only a host-side handle: passing it to a kernel from host code would
+// hand the kernel a host address. The device address is fetched with cudaGetSymbolAddress, once per
+// device, with that device current.
+constexpr int64_t kStaticDqFloats = FA2_BWD_STATIC_MAX_ELEMENTS;  // 16 MiB of fp32
+static __device__ __align__(256) float g_static_dq_accum[kStaticDqFloats];
+static __device__ __align__(256) int g_static_status[64];
+
+struct StaticRuntime {
+  bool ready = false;
+  float* accum = nullptr;
+  int* status = nullptr;
+};
+StaticRuntime g_static_rt[kMaxDevices];
+
+int get_static_runtime(int device, StaticRuntime** out) {
+  if (device < 0 || device >= kMaxDevices) return fail(FA2_E_VALUE, "device index %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_mu);
+  StaticRuntime& rt = g_static_rt[device];
+  if (!rt.ready) {
+    int cc_major = 0;
+    cudaError_t e = cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, device);
+    if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
+    if (cc_major != 10) return fail(FA2_E_RUNTIME, "this library is built for sm_100a only");
+    if (g_encode == nullptr) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+      if (e != cudaSuccess || fn == nullptr)
+        return fail(FA2_E_RUNTIME, "cuTensorMapEncodeTiled is not available from the driver");
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    void* accum = nullptr;
+    void* status = nullptr;
+    e = cudaGetSymbolAddress(&accum, g_static_dq_accum);
+    if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "cudaGetSymbolAddress(accumulator): %s", cudaGetErrorString(e));
+    e = cudaGetSymbolAddress(&status, g_static_status);
+    if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "cudaGetSymbolAddress(status): %s", cudaGetErrorString(e));
+    rt.accum = static_cast<float*>(accum);
+    rt.status = static_cast<int*>(status);
+    rt.ready = true;
+  }
+  *out = &rt;
+  return FA2_OK;
+}
+
+int bwd_static_impl(const fa2_bwd_args* a, void* stream_v) {
+  if (a == nullptr) return fail(FA2_E_VALUE, "args is null");
+  if (a->dtype != FA2_F16 && a->dtype != FA2_BF16) return fail(FA2_E_TYPE, "q, k, v must be float16 or bfloat16");
+  if (a->cu_seqlens_q != nullptr || a->cu_seqlens_k != nullptr)
+    return fail(FA2_E_VALUE, "fa2_bwd_static takes dense [B, S, H, D] tensors only");
+  const int d = a->head_dim;
+  if (d != 64 && d != 128) return fail(FA2_E_VALUE, "head dim %d is not built for sm_100a (64 and 128 are)", d);
+  if (a->heads_k <= 0 || a->heads % a->heads_k != 0)
+    return fail(FA2_E_VALUE, "num_heads (%d) must be a multiple of num_heads_k (%d)", a->heads, a->heads_k);
+  if (a->batch <= 0 || a->heads <= 0 || a->batch > 65535 || a->heads > 65535 || a->seqlen_q <= 0 || a->seqlen_k <= 0)
+    return fail(FA2_E_VALUE, "fa2_bwd_static needs positive batch, heads and sequence lengths");
+  if ((a->which & 3) != 3) return fail(FA2_E_VALUE, "fa2_bwd_static always produces dQ, dK and dV (which = 3)");
+  const int64_t n_dq = static_cast<int64_t>(a->batch) * a->seqlen_q * a->heads * d;
+  if (n_dq > kStaticDqFloats)
+    return fail(FA2_E_VALUE,
+                "fa2_bwd_static: B*Sq*H*D = %lld exceeds the built-in accumulator of %lld elements; use fa2_bwd with "
+                "a caller-provided dq_accum",
+                static_cast<long long>(n_dq), static_cast<long long>(kStaticDqFloats));
+  if (a->q == nullptr || a->k == nullptr || a->v == nullptr || a->dout == nullptr || a->lse == nullptr ||
+      a->delta == nullptr || a->dq == nullptr || a->dk == nullptr || a->dv == nullptr)
+    return fail(FA2_E_VALUE, "q, k, v, dout, lse, delta, dq, dk and dv must be non-null");
+  int rc;
+  if ((rc = check_layout(a->q, a->q_stride, 3, "q")) != FA2_OK) return rc;
+  if ((rc = check_layout(a->k, a->k_stride, 3, "k")) != FA2_OK) return rc;
+  if ((rc = check_layout(a->v, a->v_stride, 3, "v")) != FA2_OK) return rc;
+  if ((rc = check_layout(a->dout, a->do_stride, 3, "dout")) != FA2_OK) return rc;
+  if (reinterpret_cast<uintptr_t>(a->dq) % 16 || reinterpret_cast<uintptr_t>(a->dk) % 16 ||
+      reinterpret_cast<uintptr_t>(a->dv) % 16)
+    return fail(FA2_E_VALUE, "dq, dk and dv must be 16-byte aligned");
+  int device = 0;
+  cudaGetDevice(&device);
+  StaticRuntime* rt = nullptr;
+  if ((rc = get_static_runtime(device, &rt)) != FA2_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  fa2::BwdParams p;
+  memset(&p, 0, sizeof(p));
+  const int64_t rows_q = a->seqlen_q, rows_k = a->seqlen_k, nbatch = a->batch;
+  const int64_t hd = static_cast<int64_t>(a->heads) * d, hkd = static_cast<int64_t>(a->heads_k) * d;
+  if ((rc = make_map(&p.tm_q, a->q, a->dtype, 2, d, a->heads, rows_q, nbatch, a->q_stride[2], a->q_stride[1],
+                     a->q_stride[0], 64, 128, "q")) != FA2_OK) return rc;
+  if ((rc = make_map(&p.tm_do, a->dout, a->dtype, 2, d, a->heads, rows_q, nbatch, a->do_stride[2], a->do_stride[1],
+                     a->do_stride[0], 64, 128, "dout")) != FA2_OK) return rc;
+  if ((rc = make_map(&p.tm_k, a->k, a->dtype, 2, d, a->heads_k, rows_k, nbatch, a->k_stride[2], a->k_stride[1],
+                     a->k_stride[0], 64, 128, "k")) != FA2_OK) return rc;
+  if ((rc = make_map(&p.tm_v, a->v, a->dtype, 2, d, a->heads_k, rows_k, nbatch, a->v_stride[2], a->v_stride[1],
+                     a->v_stride[0], 64, 128, "v")) != FA2_OK) return rc;
+  if ((rc = make_map(&p.tm_dk, a->dk, a->dtype, 2, d, a->heads_k, rows_k, nbatch, d, hkd, rows_k * hkd, 64, 128,
+                     "dk")) != FA2_OK) return rc;
+  if ((rc = make_map(&p.tm_dv, a->dv, a->dtype, 2, d, a->heads_k, rows_k, nbatch, d, hkd, rows_k * hkd, 64, 128,
+                     "dv")) != FA2_OK) return rc;
+  if ((rc = make_map(&p.tm_dqa, rt->accum, 2, 4, d, a->heads, rows_q, nbatch, d, hd, rows_q * hd, 32, 128,
+                     "static dq accumulator")) != FA2_OK) return rc;
+  p.lse = a->lse;
+  p.delta = a->delta;
+  p.dk_ptr = a->dk;
+  p.dv_ptr = a->dv;
+  const int64_t sq_pad = (a->seqlen_q + 127) / 128 * 128;
+  p.lse_head_stride = a->seqlen_q;
+  p.lse_batch_stride = static_cast<int64_t>(a->heads) * a->seqlen_q;
+  p.delta_head_stride = sq_pad;
+  p.delta_batch_stride = static_cast<int64_t>(a->heads) * sq_pad;
+  p.dkv_row_stride = hkd;
+  p.dkv_head_stride = d;
+  p.dkv_batch_stride = rows_k * hkd;
+  p.batch = a->batch;
+  p.heads = a->heads;
+  p.heads_k = a->heads_k;
+  p.group = a->heads / a->heads_k;
+  p.seqlen_q = a->seqlen_q;
+  p.seqlen_k = a->seqlen_k;
+  p.num_nblk = (a->seqlen_k + 127) / 128;
+  const Windows w = normalise_windows(a->window_left, a->window_right, a->causal != 0, a->seqlen_k, false);
+  p.window_left = w.left;
+  p.window_right = w.right;
+  p.which = 3;
+  p.scale = a->softmax_scale;
+  p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  p.status = rt->status;
+
+  // The array keeps whatever the previous call left: the part this call adds into starts at zero.
+  cudaError_t e = cudaMemsetAsync(rt->accum, 0, static_cast<size_t>(n_dq) * 4, stream);
+  if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "memset failed: %s", cudaGetErrorString(e));
+  if ((e = fa2::launch_bwd(p, d, a->dtype == FA2_BF16, stream)) != cudaSuccess)
+    return fail(FA2_E_RUNTIME, "backward launch failed: %s", cudaGetErrorString(e));
+  if ((e = fa2::launch_dq_convert(rt->accum, a->dq, n_dq, a->softmax_scale, a->dtype == FA2_BF16, stream)) != cudaSuccess)
+    return fail(FA2_E_RUNTIME, "dq convert launch failed: %s", cudaGetErrorString(e));
+  return FA2_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -453,6 +599,8 @@ int64_t fa2_bwd_workspace_bytes(const fa2_bwd_args* args) {
 }
 
 int fa2_bwd(const fa2_bwd_args* args, void* stream) { return bwd_impl(args, stream); }
+
+int fa2_bwd_static(const fa2_bwd_args* args, void* stream) { return bwd_static_impl(args, stream); }
 
 
 int fa2_fwd(const fa2_fwd_args* args, void* stream) { return fwd_common(args, stream, false); }

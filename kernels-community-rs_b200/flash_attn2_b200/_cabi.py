@@ -12,6 +12,7 @@ _LIB_DIR = Path(__file__).resolve().parent.parent / "lib"
 LIB_PATH = _LIB_DIR / "libfa2_b200.so"
 
 FA2_F16, FA2_BF16 = 0, 1
+FA2_BWD_STATIC_MAX_ELEMENTS = 4194304
 
 
 class FwdArgs(C.Structure):
@@ -59,6 +60,7 @@ class BwdArgs(C.Structure):
 # Every symbol include/fa2_b200.h declares; the CPU test suite checks that the library exports them.
 EXPORTS = (
     "fa2_fwd", "fa2_varlen_fwd", "fa2_bwd_preprocess", "fa2_bwd_workspace_bytes", "fa2_bwd",
+    "fa2_bwd_static",
     "fa2_last_error", "fa2_device_status", "fa2_sm_count",
 )
 
@@ -85,6 +87,9 @@ def load() -> C.CDLL:
             lib.fa2_bwd.restype = C.c_int
             lib.fa2_bwd_workspace_bytes.argtypes = [C.POINTER(BwdArgs)]
             lib.fa2_bwd_workspace_bytes.restype = C.c_int64
+        if hasattr(lib, "fa2_bwd_static"):
+            lib.fa2_bwd_static.argtypes = [C.POINTER(BwdArgs), C.c_void_p]
+            lib.fa2_bwd_static.restype = C.c_int
         lib.fa2_device_status.argtypes = [C.c_int]
         lib.fa2_device_status.restype = C.c_int
         lib.fa2_sm_count.argtypes = [C.c_int]
