@@ -372,25 +372,28 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     const uint32_t t_dp = tmem + lane_addr + Cfg::kTmemDP + wg * 64;
     const int kpos = ti.n0 + key_in;
     bool ok = true;
-    for (int it = 0; it < n_iter; ++it) {
+    // LSE (log2 domain) and delta of one query block: thread ct < 128 loads LSE of row ct, the others
+    // delta of row ct - 128; rows past the sequence give P = 0. The value for iteration it + 1 is
+    // requested while iteration it computes, so its latency never sits in front of phase A.
+    auto load_stat = [&](int it) -> float {
       const int hq = ti.hk * p.group + it / ti.n_m;
+      const int q = (ti.m_start + it % ti.n_m) * kBlk + (ct & 127);
+      if (ct < kBlk) {
+        float v = INFINITY;
+        if (q < ti.sq) v = p.lse[ti.bq * p.lse_batch_stride + hq * p.lse_head_stride + ti.q_row0 + q] * kLog2e;
+        return v;
+      }
+      float v = 0.f;
+      if (q < ti.sq)
+        v = p.delta[ti.bq * p.delta_batch_stride + hq * p.delta_head_stride + ti.q_row0 + ti.b * p.delta_seq_pad + q];
+      return v;
+    };
+    float stat_next = n_iter > 0 ? load_stat(0) : 0.f;
+    for (int it = 0; it < n_iter; ++it) {
       const int m0 = (ti.m_start + it % ti.n_m) * kBlk;
       float* stat = s_stat + (it & 1) * (2 * kBlk);
-      {
-        // Stage this block's LSE (log2 domain) and delta; rows past the sequence give P = 0.
-        const int r = ct & 127;
-        const int q = m0 + r;
-        float val;
-        if (ct < kBlk) {
-          val = INFINITY;
-          if (q < ti.sq) val = p.lse[ti.bq * p.lse_batch_stride + hq * p.lse_head_stride + ti.q_row0 + q] * kLog2e;
-        } else {
-          val = 0.f;
-          if (q < ti.sq)
-            val = p.delta[ti.bq * p.delta_batch_stride + hq * p.delta_head_stride + ti.q_row0 + ti.b * p.delta_seq_pad + q];
-        }
-        stat[ct] = val;
-      }
+      stat[ct] = stat_next;
+      if (it + 1 < n_iter) stat_next = load_stat(it + 1);
       if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 0);
       mbar_arrive(stat_full);
       if (!mbar_wait(stat_full, it & 1, ctl, kWaitBwd + 15)) { ok = false; break; }
@@ -478,30 +481,26 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         tc_fence_after();
         uint16_t* grow = gptr + ti.bq * p.dkv_batch_stride + static_cast<int64_t>(ti.k_row0 + kpos) * p.dkv_row_stride +
                          ti.hk * p.dkv_head_stride;
+        uint32_t acc[D];
+        if (n_iter > 0) {
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t acc[32];
-          if (n_iter > 0) {
-            tmem_ld32(t_acc + c * 32, acc);
-            tmem_wait_ld();
-          } else {
+          for (int c = 0; c < D / 32; ++c) tmem_ld32(t_acc + c * 32, acc + c * 32);
+          tmem_wait_ld();
+        } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] = 0;
-          }
-          uint32_t w[16];
+          for (int i = 0; i < D; ++i) acc[i] = 0;
+        }
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            w[i] = pack2<BF16>(__uint_as_float(acc[2 * i]) * mul, __uint_as_float(acc[2 * i + 1]) * mul);
+        for (int c = 0; c < D / 8; ++c) {  // 16-byte chunks of the row
+          uint4 w;
+          w.x = pack2<BF16>(__uint_as_float(acc[8 * c]) * mul, __uint_as_float(acc[8 * c + 1]) * mul);
+          w.y = pack2<BF16>(__uint_as_float(acc[8 * c + 2]) * mul, __uint_as_float(acc[8 * c + 3]) * mul);
+          w.z = pack2<BF16>(__uint_as_float(acc[8 * c + 4]) * mul, __uint_as_float(acc[8 * c + 5]) * mul);
+          w.w = pack2<BF16>(__uint_as_float(acc[8 * c + 6]) * mul, __uint_as_float(acc[8 * c + 7]) * mul);
           if (tma_store) {
-            uint8_t* rowp = stage + (c / 2) * (kBlk * 128) + key_in * 128;
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              *reinterpret_cast<uint4*>(rowp + ((((c & 1) * 4 + q) ^ (key_in & 7)) << 4)) =
-                  make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+            *reinterpret_cast<uint4*>(stage + (c / 8) * (kBlk * 128) + key_in * 128 + (((c & 7) ^ (key_in & 7)) << 4)) = w;
           } else if (kpos < ti.sk) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              *reinterpret_cast<uint4*>(grow + c * 32 + q * 8) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+            *reinterpret_cast<uint4*>(grow + c * 8) = w;
           }
         }
         if (tma_store) {
@@ -614,7 +613,7 @@ cudaError_t launch_one(const BwdParams& p, int num_ctas, cudaStream_t stream) {
 
 }  // namespace
 
-cudaError_t launch_bwd(const BwdParams& p, int head_dim, bool bf16, cudaStream_t stream) {
+cudaError_t launch_bwd(const BwdParams& p, int head_dim, bool bf16, int /*num_sms*/, cudaStream_t stream) {
   const int num_ctas = p.num_nblk * p.batch * p.heads_k;
   if (num_ctas <= 0) return cudaSuccess;
   if (head_dim == 128) return bf16 ? launch_one<128, true>(p, num_ctas, stream) : launch_one<128, false>(p, num_ctas, stream);

@@ -11,6 +11,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 namespace {
@@ -38,6 +39,17 @@ struct Runtime {
   int* status = nullptr;  // device status word
 };
 constexpr int kMaxDevices = 64;
+constexpr int kStatusWords = 64;
+constexpr int kCounterBase = 16, kCounterSlots = 32;
+std::atomic<unsigned> g_launch_seq{0};
+
+// A zeroed device work counter for one backward launch. Launches take the slots in turn, so only
+// more than kCounterSlots launches in flight at once on one device could share one.
+int* next_counter(int* status_words, cudaStream_t stream) {
+  int* c = status_words + kCounterBase + (g_launch_seq.fetch_add(1) % kCounterSlots);
+  cudaMemsetAsync(c, 0, sizeof(int), stream);
+  return c;
+}
 Runtime g_rt[kMaxDevices];
 std::mutex g_mu;
 EncodeTiledFn g_encode = nullptr;
@@ -63,9 +75,10 @@ int get_runtime(int device, Runtime** out) {
         return fail(FA2_E_RUNTIME, "cuTensorMapEncodeTiled is not available from the driver");
       g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
-    e = cudaMalloc(&rt.status, sizeof(int));
+    // word 0: kernel status; words 16..47: work counters handed to successive backward launches
+    e = cudaMalloc(&rt.status, kStatusWords * sizeof(int));
     if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "cudaMalloc(status): %s", cudaGetErrorString(e));
-    cudaMemset(rt.status, 0, sizeof(int));
+    cudaMemset(rt.status, 0, kStatusWords * sizeof(int));
     rt.sm_count = prop.multiProcessorCount;
     rt.cc_major = prop.major;
     rt.ready = true;
@@ -428,11 +441,12 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
   p.scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.status = rt->status;
+  p.tile_counter = next_counter(rt->status, stream);
 
   if (want_dq && (e = cudaMemsetAsync(a->dq_accum, 0, n_dq * 4, stream)) != cudaSuccess)
     return fail(FA2_E_RUNTIME, "memset failed: %s", cudaGetErrorString(e));
   if (a->ev_kernel_start != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_kernel_start), stream);
-  e = fa2::launch_bwd(p, d, a->dtype == FA2_BF16, stream);
+  e = fa2::launch_bwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream);
   if (a->ev_kernel_stop != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_kernel_stop), stream);
   if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "backward launch failed: %s", cudaGetErrorString(e));
   if (want_dq && (e = fa2::launch_dq_convert(static_cast<const float*>(a->dq_accum), a->dq, n_dq, a->softmax_scale,
@@ -463,6 +477,7 @@ struct StaticRuntime {
   bool ready = false;
   float* accum = nullptr;
   int* status = nullptr;
+  int sm_count = 0;
 };
 StaticRuntime g_static_rt[kMaxDevices];
 
@@ -489,6 +504,8 @@ int get_static_runtime(int device, StaticRuntime** out) {
     if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "cudaGetSymbolAddress(accumulator): %s", cudaGetErrorString(e));
     e = cudaGetSymbolAddress(&status, g_static_status);
     if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "cudaGetSymbolAddress(status): %s", cudaGetErrorString(e));
+    e = cudaDeviceGetAttribute(&rt.sm_count, cudaDevAttrMultiProcessorCount, device);
+    if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
     rt.accum = static_cast<float*>(accum);
     rt.status = static_cast<int*>(status);
     rt.ready = true;
@@ -576,11 +593,12 @@ int bwd_static_impl(const fa2_bwd_args* a, void* stream_v) {
   p.scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.status = rt->status;
+  p.tile_counter = next_counter(rt->status, stream);
 
   // The array keeps whatever the previous call left: the part this call adds into starts at zero.
   cudaError_t e = cudaMemsetAsync(rt->accum, 0, static_cast<size_t>(n_dq) * 4, stream);
   if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "memset failed: %s", cudaGetErrorString(e));
-  if ((e = fa2::launch_bwd(p, d, a->dtype == FA2_BF16, stream)) != cudaSuccess)
+  if ((e = fa2::launch_bwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream)) != cudaSuccess)
     return fail(FA2_E_RUNTIME, "backward launch failed: %s", cudaGetErrorString(e));
   if ((e = fa2::launch_dq_convert(rt->accum, a->dq, n_dq, a->softmax_scale, a->dtype == FA2_BF16, stream)) != cudaSuccess)
     return fail(FA2_E_RUNTIME, "dq convert launch failed: %s", cudaGetErrorString(e));

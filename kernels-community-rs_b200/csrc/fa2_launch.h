@@ -8,8 +8,9 @@ namespace fa2 {
 // Dense and packed (varlen) forward; head_dim is 64 or 128.
 cudaError_t launch_fwd(const FwdParams& p, int head_dim, bool bf16, int num_sms, cudaStream_t stream);
 
-// dQ / dK / dV for head_dim 64 or 128; the fp32 dQ accumulator behind p.tm_dqa must be zero.
-cudaError_t launch_bwd(const BwdParams& p, int head_dim, bool bf16, cudaStream_t stream);
+// dQ / dK / dV for head_dim 64 or 128; the fp32 dQ accumulator behind p.tm_dqa and the work counter
+// p.tile_counter must be zero.
+cudaError_t launch_bwd(const BwdParams& p, int head_dim, bool bf16, int num_sms, cudaStream_t stream);
 
 // delta = rowsum(dO * O) into the padded layouts (dense [B,H,Sq_pad], packed [H,total_q+128*B]).
 cudaError_t launch_bwd_preprocess(const PreprocessParams& p, cudaStream_t stream);

@@ -63,6 +63,7 @@ struct BwdParams {
   int which;                            // bit 0: dQ, bit 1: dK and dV
   float scale, scale_log2;
   int* status;
+  int* tile_counter;                    // device work counter of this launch, zero at launch
 };
 
 struct PreprocessParams {
