@@ -14,6 +14,7 @@ enum WaitSite : int {
   kWaitMmaKVFull = 22,
   kWaitMmaPFull = 23,
   kWaitMmaOFree = 24,
+  kWaitMmaSFree = 25,
   kWaitSoftmaxSFull = 31,
   kWaitSoftmaxPvDone = 32,
   kWaitEpiFinal = 41,

@@ -1,21 +1,24 @@
 // FlashAttention-2 forward for sm_100a (B200).
 //
 // One persistent CTA per SM walks a longest-first list of work tiles. A work tile is 256 query
-// rows of one (batch, head): two 128-row "stages" that ping-pong so the tensor core always has
-// one stage's MMA to run while the other stage's softmax is in flight.
+// rows of one (batch, head): two 128-row "stages" that run independently of each other and share
+// the K/V tiles in shared memory.
 //
-//   warps 0-3    stage 0 } softmax: tcgen05.ld one S row per thread -> mask, row max, exp2, row sum ->
-//   warps 4-7    stage 1 }   bf16/fp16 P written back over S in TMEM (tcgen05.st); O in TMEM is rescaled
-//                            only when the row max grew by more than 2^8. At the end of a tile the same
-//                            warps run the stage's epilogue: O / l -> 16-bit -> swizzled smem -> TMA store
+//   warps 0-3    stage 0 } softmax: tcgen05.ld one S row per thread (the S region of TMEM is handed back
+//   warps 4-7    stage 1 }   to the MMA warp at once, so the next Q K^T runs under this softmax) -> mask,
+//                            row max, exp2, row sum -> bf16/fp16 P written to shared memory in pieces, as the
+//                            K-major swizzled A operand of P V; O in TMEM is rescaled only when the row max
+//                            grew by more than 2^8. At the end of a tile the same warps run the stage's
+//                            epilogue: O / l -> 16-bit -> swizzled smem (the P buffer) -> TMA store
 //                            (predicated stores on ragged packed tiles), LSE = (m + log2 l) ln 2.
-//   warp 8       mma      : one thread issues tcgen05.mma; S = Q K^T (smem x smem) into TMEM,
-//                           O += P V (P read from TMEM, V from smem as an MN-major operand)
-//   warp 9       loader   : TMA (cp.async.bulk.tensor, 128B swizzle) Q stages + K/V ring
+//   warp 8, 10   mma      : one thread per stage issues tcgen05.mma; S = Q K^T (smem x smem) into TMEM one
+//                           key tile ahead, O += P V (smem x smem, V as an MN-major operand) piece by piece
+//   warp 9       loader   : TMA (cp.async.bulk.tensor, 128B swizzle) Q stages + K/V ring in the order
+//                           K(0) K(1) V(0) K(2) V(1) ...
 //
-// The Q stage buffers are released by the MMA thread as soon as the tile's last Q K^T has been read,
-// and the output is staged in its own smem tiles, so the next tile's Q load and first Q K^T overlap
-// the epilogue of the current tile.
+// A stage never waits for the other one: each has its own issuing thread, barriers and counters, and a
+// K/V ring slot is released by one commit of each issuer, so stage 0 may already work on the next tile
+// while stage 1 finishes the current one.
 //
 // Replaces the reference kernels flash_attn_fwd / varlen_fwd
 // (flash-attn2-rs/src/device/forward/dense.rs:472-590, forward/mod.rs:1162-1407,
@@ -25,6 +28,9 @@
 #include "fa2_params.h"
 #include "fa2_launch.h"
 
+#ifndef FA2_PQ
+#define FA2_PQ 4
+#endif
 #ifndef FA2_POLY_PAIRS
 #define FA2_POLY_PAIRS 0
 #endif
@@ -48,10 +54,12 @@ namespace {
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
 constexpr int kThreads = 384;   // 8 softmax warps + one warpgroup holding the MMA and the loader warp
-constexpr int kMmaWarp = 8;
+constexpr int kMmaWarp = 8;   // issues the MMAs of stage 0
+constexpr int kMmaWarp1 = 10;  // issues the MMAs of stage 1
 constexpr int kLoadWarp = 9;
 constexpr int kSoftmaxRegs = 200;
 constexpr int kOtherRegs = 104;
+constexpr int kPQ = FA2_PQ;                        // P is handed to the MMA warp in kPQ pieces of kBlockN / kPQ keys
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain
 constexpr int kPolyPairs = FA2_POLY_PAIRS;    // of every 4 score pairs, how many take exp2 on the FMA pipe
 
@@ -62,9 +70,13 @@ struct FwdCfg {
   static constexpr int kSlots = (D == 128) ? 3 : 6;        // K/V ring depth
   static constexpr int kQOff = 0;
   static constexpr int kKVOff = 2 * kTileBytes;
-  static constexpr int kOOff = kKVOff + kSlots * kTileBytes;  // O staging for the TMA stores, one tile per stage
-  static constexpr int kBarOff = kOOff + 2 * kTileBytes;
-  static constexpr int kNumBars = 2 * kSlots + 18;
+  // One buffer per stage that holds P (128 x 128 16-bit, the A operand of P V) during the key loop and
+  // the output tile for the TMA store in the epilogue.
+  static constexpr int kPBytes = kBlockM * kBlockN * 2;
+  static constexpr int kStageBufBytes = kTileBytes > kPBytes ? kTileBytes : kPBytes;
+  static constexpr int kOOff = kKVOff + kSlots * kTileBytes;
+  static constexpr int kBarOff = kOOff + 2 * kStageBufBytes;
+  static constexpr int kNumBars = 2 * kSlots + 18 + 2 * kPQ;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;  // tmem slot, abort flag
   static constexpr int kSmemBytes = kMiscOff + 32;  // the dynamic window must start 1024-aligned
   static constexpr uint32_t kTmemS0 = 0, kTmemS1 = 128, kTmemO0 = 256, kTmemO1 = 256 + D;
@@ -160,7 +172,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   uint64_t* q_full = bars + 2 * Cfg::kSlots;  // every array below is [2], one per stage
   uint64_t* q_empty = q_full + 2;
   uint64_t* s_full = q_full + 4;
-  uint64_t* p_full = q_full + 6;
+  uint64_t* s_free = q_full + 16;        // S_s has been read out of TMEM: the next Q K^T may overwrite it
+  uint64_t* p_full = q_full + 18;        // [2][kPQ]: piece q of P_s is in shared memory
   uint64_t* pv_done = q_full + 8;
   uint64_t* o_free = q_full + 10;        // O_s has been read out of TMEM
   uint64_t* epi_full = q_full + 12;      // all 128 rows of O_s are staged in smem
@@ -172,20 +185,29 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const WaitCtl ctl{abort_flag, p.status};
+#ifdef FA2_TIMING
+  if (tid == 0 && blockIdx.x == 0) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+    g_fwd_timing[1000] = clock64();
+    g_fwd_timing[1001] = static_cast<long long>(gt);
+  }
+#endif
 
   if (tid == 0) {
     *abort_flag = 0;
     for (int i = 0; i < Cfg::kSlots; ++i) {
       mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&kv_empty[i], 2);  // one commit per stage cursor of the MMA warp
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&q_full[s], 1);
       mbar_init(&q_empty[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], kBlockM);
+      for (int q = 0; q < kPQ; ++q) mbar_init(&p_full[s * kPQ + q], kBlockM);
       mbar_init(&pv_done[s], 1);
       mbar_init(&o_free[s], kBlockM);
+      mbar_init(&s_free[s], kBlockM);
       mbar_init(&epi_full[s], kBlockM);
       mbar_init(&o_stage_free[s], 1);
     }
@@ -214,9 +236,20 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_s = tmem + lane_addr + (s == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1);
     const uint32_t t_o = tmem + lane_addr + (s == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
-    uint8_t* stage_smem = s_o + s * Cfg::kTileBytes;
+    uint8_t* stage_smem = s_o + s * Cfg::kStageBufBytes;
+    // P of this stage as the K-major, 128-byte swizzled A operand of P V: key chunk c (8 keys, 16 bytes) of
+    // row r sits in atom c / 8 at byte 128 r + 16 ((c % 8) ^ (r % 8)).
+    const uint32_t p_row = smem_u32(stage_smem) + row_in * 128;
+    const uint32_t p_swz = static_cast<uint32_t>(row_in & 7) << 4;
+    auto store_p_chunk = [&](const int c, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+      const uint32_t addr = p_row + (c >> 3) * (kBlockM * 128) + ((static_cast<uint32_t>(c & 7) << 4) ^ p_swz);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+    };
     const bool fancy = (p.softcap > 0.f) || (p.alibi != nullptr) || (p.scale_log2 < 0.f);
-    uint32_t n_sfull = 0, n_pv = 0, n_store = 0;
+    uint32_t n_sfull = 0, n_pv = 0, n_store = 0, n_first = 0;
+#ifdef FA2_TIMING
+    int tm_tile = 0;
+#endif
     for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
       const Tile ti = get_tile(p, t);
       if (!ti.valid) continue;
@@ -240,17 +273,12 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
 #endif
         ++n_sfull;
         tc_fence_after();
-#if defined(FA2_EXP) && FA2_EXP == 3
-        { const long long tw = clock64(); while (clock64() - tw < 1500) { } }
-        tc_fence_before();
-        mbar_arrive(&p_full[s]);
-        ++n_pv;
-        continue;
-#endif
         uint32_t sr[kBlockN];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, sr + c * 32);
         tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&s_free[s]);  // the scores live in registers from here on
 #ifdef FA2_TIMING
         if (tm_on) FA2_STAMP(tm_base + 2);
 #endif
@@ -334,9 +362,20 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             l *= alpha;
           }
         }
-        if (j > nb_s && __any_sync(0xffffffffu, grow)) {
-          // O of this stage is only touched by PV(j-1), which has to be complete.
+        if (j > nb_s) {
+          // P V(j-1) has to be complete: it reads the P buffer that this iteration overwrites, and it is the
+          // only operation that touches O of this stage.
           if (!mbar_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitSoftmaxPvDone)) { ok = false; break; }
+        } else {
+          // First iteration of a tile: the TMA store of the previous tile must have read the buffer.
+          if (row_in == 0) {
+            tma_wait_group_read<0>();
+            mbar_arrive(&o_stage_free[s]);
+          }
+          if (!mbar_wait(&o_stage_free[s], n_first & 1, ctl, kWaitEpiFinal)) { ok = false; break; }
+          ++n_first;
+        }
+        if (j > nb_s && __any_sync(0xffffffffu, grow)) {
           tc_fence_after();
 #pragma unroll
           for (int c = 0; c < D / 16; ++c) {
@@ -357,6 +396,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2);
           const uint64_t nm2 = pack_f32x2(-m, -m);  // m is finite here: the tile has no masked score
           uint64_t acc0 = pack_f32x2(0.f, 0.f), acc1 = acc0;
+          constexpr int kPieceCols = kBlockN / kPQ;  // 32 scores -> 16 packed TMEM columns
 #pragma unroll
           for (int i = 0; i < kBlockN; i += 8) {
             float x[8];
@@ -380,6 +420,13 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             acc1 = add2(acc1, pack_f32x2(x[6], x[7]));
 #pragma unroll
             for (int q = 0; q < 4; ++q) sr[i / 2 + q] = pack2<BF16>(x[2 * q], x[2 * q + 1]);
+            // The eight probabilities just packed are one 16-byte chunk of this row of P; a piece is
+            // announced to the MMA warp as soon as its last chunk is written.
+            store_p_chunk(i / 8, sr[i / 2], sr[i / 2 + 1], sr[i / 2 + 2], sr[i / 2 + 3]);
+            if (i % kPieceCols == kPieceCols - 8) {
+              fence_proxy_async_smem();
+              mbar_arrive(&p_full[s * kPQ + i / kPieceCols]);
+            }
           }
           float a0, a1;
           unpack_f32x2(add2(acc0, acc1), a0, a1);
@@ -405,30 +452,28 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
 #ifdef FA2_TIMING
         if (tm_on) FA2_STAMP(tm_base + 4);
 #endif
-        tmem_st32(t_s, sr);
-        tmem_st32(t_s + 32, sr + 32);
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(&p_full[s]);
+        if (fancy || need_mask) {
+#pragma unroll
+          for (int c = 0; c < kBlockN / 8; ++c) store_p_chunk(c, sr[4 * c], sr[4 * c + 1], sr[4 * c + 2], sr[4 * c + 3]);
+          fence_proxy_async_smem();
+#pragma unroll
+          for (int q = 0; q < kPQ; ++q) mbar_arrive(&p_full[s * kPQ + q]);
+        }
 #ifdef FA2_TIMING
         if (tm_on) FA2_STAMP(tm_base + 5);
 #endif
         ++n_pv;
       }
       if (!ok) break;
+#ifdef FA2_TIMING
+      if (row_in == 0 && tm_tile < 16) FA2_STAMP(800 + tm_tile * 10 + 3 + s * 3);
+#endif
       // ---- epilogue of this stage: O / l -> 16-bit -> swizzled smem -> one TMA store.
       // A ragged tile of a packed batch (rows of the next sequence follow) uses predicated stores.
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.o_ptr) + ti.bq * p.o_batch_stride +
                        static_cast<int64_t>(ti.q_row0 + row) * p.o_row_stride + ti.h * p.o_head_stride;
       const bool tma_store = (p.cu_q == nullptr) || (r_lo + kBlockM <= ti.sq);
       if (ne_s > nb_s) {
-        if (tma_store) {
-          if (row_in == 0) {
-            tma_wait_group_read<0>();  // the store of the previous tile has read the staging tile
-            mbar_arrive(&o_stage_free[s]);
-          }
-          if (!mbar_wait(&o_stage_free[s], n_store & 1, ctl, kWaitEpiFinal)) break;
-        }
         if (!mbar_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitEpiPvDone)) break;
         tc_fence_after();
         uint32_t orr[D];
@@ -437,6 +482,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(&o_free[s]);
+#ifdef FA2_TIMING
+        if (row_in == 0 && tm_tile < 16) FA2_STAMP(800 + tm_tile * 10 + 4 + s * 3);
+#endif
         const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
 #pragma unroll
         for (int c = 0; c < D / 8; ++c) {  // 16-byte chunks of the row
@@ -473,6 +521,10 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           for (int q = 0; q < D / 8; ++q) *reinterpret_cast<uint4*>(orow + q * 8) = make_uint4(0, 0, 0, 0);
         }
       }
+#ifdef FA2_TIMING
+      if (row_in == 0 && tm_tile < 16) FA2_STAMP(800 + tm_tile * 10 + 5 + s * 3);
+      ++tm_tile;
+#endif
       if (row < ti.sq) {
         const float lse = (l > 0.f) ? (m + lg2(l)) * 0.6931471805599453f : INFINITY;
         p.lse_ptr[ti.bq * p.lse_batch_stride + ti.h * p.lse_head_stride + ti.q_row0 + row] = lse;
@@ -513,13 +565,14 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
                         ti.q_row0 + ti.m0 + s * kBlockM, ti.bq);
           return true;
         };
+        // Ring order K(jlo), K(jlo+1), V(jlo), K(jlo+2), V(jlo+1), ...: Q K^T runs one key tile ahead of P V.
         ok = load_q(0);
+        if (ti.jlo < ti.jhi && ok) ok = load_kv(&p.tm_k, ti.k_row0 + ti.jlo * kBlockN, ti.hk, ti.bq);
+        if (ok) ok = load_q(1);
         for (int j = ti.jlo; j < ti.jhi && ok; ++j) {
-          ok = load_kv(&p.tm_k, ti.k_row0 + j * kBlockN, ti.hk, ti.bq);
-          if (j == ti.jlo && ok) ok = load_q(1);
+          if (j + 1 < ti.jhi) ok = load_kv(&p.tm_k, ti.k_row0 + (j + 1) * kBlockN, ti.hk, ti.bq);
           if (ok) ok = load_kv(&p.tm_v, ti.k_row0 + j * kBlockN, ti.hk, ti.bq);
         }
-        if (ti.jlo >= ti.jhi && ok) ok = load_q(1);
       }
       if (!ok) {
         // Give copies that are still in flight time to land before the CTA exits.
@@ -527,7 +580,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         while (clock64() - t0 < 2000000) {
         }
       }
-    } else if (warp == kMmaWarp && lane == 0) {
+    } else if ((warp == kMmaWarp || warp == kMmaWarp1) && lane == 0) {
       // ---------------------------------------------------------------- mma issuer
       // Descriptors are built once; inside the loops an operand address is one 64-bit add of a
       // compile-time constant (descriptor address field is in 16-byte units), so that the single
@@ -540,99 +593,86 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
       const uint64_t q_desc = make_smem_desc(smem_u32(s_q), 16, 1024);                 // K-major A
       const uint64_t k_desc = make_smem_desc(smem_u32(s_kv), 16, 1024);                // K-major B
       const uint64_t v_desc = make_smem_desc(smem_u32(s_kv), kBlockN * 128, 1024);     // MN-major B
-      uint32_t n_tile = 0;
+      // Each stage has its own issuing warp, and both walk the same sequence of tiles and K/V ring
+      // positions. A stage never waits for the other one: stage 0 may already run the next tile while
+      // stage 1 finishes the current one, and a piece of P V is issued while the other stage's
+      // exponentials are still in flight. A K/V slot is released by two commits, one per issuer.
+      const int s = (warp == kMmaWarp) ? 0 : 1;
+      const uint64_t a_q = q_desc + s * kTile16;
+      const uint32_t t_s = tmem + (s == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1);
+      const uint32_t t_o = tmem + (s == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
+      const uint64_t a_p = make_smem_desc(smem_u32(s_o + s * Cfg::kStageBufBytes), 16, 1024);  // P: K-major A
       uint32_t slot = 0, ring_phase = 0;  // K/V ring position of the next tile to consume
-      uint32_t n_p0 = 0, n_p1 = 0, n_q0 = 0, n_q1 = 0;
+      uint32_t n_qk = 0, n_p = 0, n_q = 0, n_tile = 0;
       bool ok = true;
+      auto advance = [&]() {
+        mma_commit(&kv_empty[slot]);
+        if (++slot == Cfg::kSlots) {
+          slot = 0;
+          ring_phase ^= 1;
+        }
+      };
       for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
         const Tile ti = get_tile(p, t);
         if (!ti.valid) continue;
-        const int nb0 = ti.nb[0], ne0 = ti.ne[0], nb1 = ti.nb[1], ne1 = ti.ne[1];
-        bool q0_ready = false, q1_ready = false;
-        // S_s = Q_s K^T over D in steps of 16 (32 bytes inside the 128-byte swizzle atom).
-        auto issue_qk = [&](const int s, const uint32_t k_slot, const bool last) -> bool {
-          bool& ready = s ? q1_ready : q0_ready;
-          if (!ready) {
-            uint32_t& nq = s ? n_q1 : n_q0;
-            if (!mbar_wait(&q_full[s], nq & 1, ctl, kWaitMmaQFull)) return false;
-            ++nq;
-            ready = true;
-          }
-          tc_fence_after();
-          const uint64_t a = q_desc + s * kTile16;
-          const uint64_t b = k_desc + k_slot * kTile16;
-          const uint32_t d_tmem = tmem + (s == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1);
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            constexpr uint32_t kAtom16 = (kBlockM * 128) >> 4;
-            const uint32_t o = (ks / 4) * kAtom16 + (ks % 4) * 2;
-            mma_ss(d_tmem, a + o, b + o, idesc_qk, ks > 0 ? 1u : 0u);
-          }
-#ifdef FA2_TIMING
-          { const uint32_t np = s ? n_p1 : n_p0; if (np >= 1 && np <= 28) FA2_STAMP(512 + s * 128 + (np - 1) * 4 + 3); }
-#endif
-          mma_commit(&s_full[s]);
-          if (last) mma_commit(&q_empty[s]);  // the Q stage may be refilled for the next tile
-          return true;
-        };
-        // O_s (+)= P_s V over the 128 keys in steps of 16 (P: 8 TMEM columns, V: 16 rows of 128 bytes).
-        auto issue_pv = [&](const int s, const uint32_t v_slot, const bool first) -> bool {
-          uint32_t& np = s ? n_p1 : n_p0;
-          if (!mbar_wait(&p_full[s], np & 1, ctl, kWaitMmaPFull)) return false;
-          ++np;
-          if (first && !mbar_wait(&o_free[s], (n_tile & 1) ^ 1, ctl, kWaitMmaOFree)) return false;
-          tc_fence_after();
-          const uint32_t d_tmem = tmem + (s == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
-          const uint32_t a_tmem = tmem + (s == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1);
-          const uint64_t b = v_desc + v_slot * kTile16;
-#ifdef FA2_TIMING
-          if (np <= 28) FA2_STAMP(512 + s * 128 + (np - 1) * 4 + 0);
-#endif
-          mma_ts(d_tmem, a_tmem, b, idesc_pv, first ? 0u : 1u);
-#pragma unroll
-          for (int ks = 1; ks < kBlockN / 16; ++ks) mma_ts(d_tmem, a_tmem + ks * 8, b + ks * (2048 >> 4), idesc_pv, 1u);
-#ifdef FA2_TIMING
-          if (np <= 28) FA2_STAMP(512 + s * 128 + (np - 1) * 4 + 1);
-#endif
-          mma_commit(&pv_done[s]);
-#ifdef FA2_TIMING
-          if (np <= 28) FA2_STAMP(512 + s * 128 + (np - 1) * 4 + 2);
-#endif
-          return true;
-        };
-        auto advance = [&]() {
-          if (++slot == Cfg::kSlots) {
-            slot = 0;
-            ring_phase ^= 1;
-          }
-        };
-
-        if (ti.jlo < ti.jhi) {
-          // Ring order is K(jlo), V(jlo), K(jlo+1), V(jlo+1), ...
-          ok = mbar_wait(&kv_full[slot], ring_phase, ctl, kWaitMmaKVFull);
-          if (ok && ti.jlo >= nb0 && ti.jlo < ne0) ok = issue_qk(0, slot, ti.jlo == ne0 - 1);
-          if (ok && ti.jlo >= nb1 && ti.jlo < ne1) ok = issue_qk(1, slot, ti.jlo == ne1 - 1);
-          if (ok) mma_commit(&kv_empty[slot]);
-          advance();
-          for (int j = ti.jlo; j < ti.jhi && ok; ++j) {
-            const uint32_t v_slot = slot, v_phase = ring_phase;
-            advance();
-            const uint32_t k_slot = slot, k_phase = ring_phase;
-            const bool has_next = (j + 1 < ti.jhi);
-            const bool a0 = j >= nb0 && j < ne0, a1 = j >= nb1 && j < ne1;
-            const bool n0 = has_next && j + 1 >= nb0 && j + 1 < ne0, n1 = has_next && j + 1 >= nb1 && j + 1 < ne1;
-            ok = mbar_wait(&kv_full[v_slot], v_phase, ctl, kWaitMmaKVFull);
-            if (ok && a0) ok = issue_pv(0, v_slot, j == nb0);
-            if (ok && has_next) ok = mbar_wait(&kv_full[k_slot], k_phase, ctl, kWaitMmaKVFull);
-            if (ok && n0) ok = issue_qk(0, k_slot, j + 1 == ne0 - 1);
-            if (ok && a1) ok = issue_pv(1, v_slot, j == nb1);
-            if (ok) mma_commit(&kv_empty[v_slot]);
-            if (ok && n1) ok = issue_qk(1, k_slot, j + 1 == ne1 - 1);
-            if (ok && has_next) {
-              mma_commit(&kv_empty[k_slot]);
-              advance();
+        const int nb = s ? ti.nb[1] : ti.nb[0], ne = s ? ti.ne[1] : ti.ne[0];
+        bool q_ready = false;
+        // S_s = Q_s K_j^T over D in steps of 16 (32 bytes inside the 128-byte swizzle atom). The S region
+        // is free as soon as the softmax warps hold the previous scores in registers.
+        auto do_k = [&](const int j) -> bool {
+          if (!mbar_wait(&kv_full[slot], ring_phase, ctl, kWaitMmaKVFull)) return false;
+          if (j >= nb && j < ne) {
+            if (!q_ready) {
+              if (!mbar_wait(&q_full[s], n_q & 1, ctl, kWaitMmaQFull)) return false;
+              ++n_q;
+              q_ready = true;
             }
+            if (!mbar_wait(&s_free[s], (n_qk & 1) ^ 1, ctl, kWaitMmaSFree)) return false;
+            ++n_qk;
+            tc_fence_after();
+            const uint64_t b = k_desc + slot * kTile16;
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+              constexpr uint32_t kAtom16 = (kBlockM * 128) >> 4;
+              const uint32_t o = (ks / 4) * kAtom16 + (ks % 4) * 2;
+              mma_ss(t_s, a_q + o, b + o, idesc_qk, ks > 0 ? 1u : 0u);
+            }
+            mma_commit(&s_full[s]);
+            if (j == ne - 1) mma_commit(&q_empty[s]);  // the Q stage may be refilled for the next tile
           }
+          advance();
+          return true;
+        };
+        // O_s (+)= P_s V_j, one piece of kBlockN / kPQ keys at a time (per step of 16 keys: 32 bytes of a
+        // P row inside its swizzle atom, 16 rows of 128 bytes of V).
+        auto do_v = [&](const int j) -> bool {
+          if (!mbar_wait(&kv_full[slot], ring_phase, ctl, kWaitMmaKVFull)) return false;
+          if (j >= nb && j < ne) {
+            const bool first = (j == nb);
+            const uint64_t b = v_desc + slot * kTile16;
+            constexpr int kStepsPerPiece = kBlockN / 16 / kPQ;
+#pragma unroll
+            for (int q = 0; q < kPQ; ++q) {
+              if (!mbar_wait(&p_full[s * kPQ + q], n_p & 1, ctl, kWaitMmaPFull)) return false;
+              if (q == 0 && first && !mbar_wait(&o_free[s], (n_tile & 1) ^ 1, ctl, kWaitMmaOFree)) return false;
+              tc_fence_after();
+#pragma unroll
+              for (int ks = q * kStepsPerPiece; ks < (q + 1) * kStepsPerPiece; ++ks) {
+                constexpr uint32_t kAtom16 = (kBlockM * 128) >> 4;
+                const uint32_t o = (ks / 4) * kAtom16 + (ks % 4) * 2;
+                mma_ss(t_o, a_p + o, b + ks * (2048 >> 4), idesc_pv, (first && ks == 0) ? 0u : 1u);
+              }
+            }
+            ++n_p;
+            mma_commit(&pv_done[s]);
+          }
+          advance();
+          return true;
+        };
+        if (ti.jlo < ti.jhi) ok = do_k(ti.jlo);
+        for (int j = ti.jlo; j < ti.jhi && ok; ++j) {
+          if (j + 1 < ti.jhi) ok = do_k(j + 1);
+          if (ok) ok = do_v(j);
         }
         ++n_tile;
       }
@@ -642,6 +682,14 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == kMmaWarp) tmem_dealloc(tmem, 512);
+#ifdef FA2_TIMING
+  if (tid == 0 && blockIdx.x == 0) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+    g_fwd_timing[1002] = clock64();
+    g_fwd_timing[1003] = static_cast<long long>(gt);
+  }
+#endif
 }
 
 template <int D, bool BF16>

@@ -53,6 +53,19 @@ struct WaitCtl {
   int* error_word;            // global memory, may be null
 };
 
+// Non-blocking probe of a phase, for a thread that polls several barriers in turn.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Upper bound of one wait in SM clock cycles (about a second at B200 clocks).
 #ifndef FA2_WAIT_LIMIT_CYCLES
 #define FA2_WAIT_LIMIT_CYCLES (1ll << 31)
