@@ -17,6 +17,7 @@ enum WaitSite : int {
   kWaitMmaSFree = 25,
   kWaitSoftmaxSFull = 31,
   kWaitSoftmaxPvDone = 32,
+  kWaitSoftmaxPair = 33,
   kWaitEpiFinal = 41,
   kWaitEpiPvDone = 42,
   kWaitBwd = 50,

@@ -96,9 +96,18 @@ struct Tile {
 
 __device__ __forceinline__ Tile get_tile(const FwdParams& p, int t) {
   Tile ti;
+  // Work tiles are listed longest first; CTA c takes list entries c, 2G-1-c, 2G+c, 4G-1-c, ... (G CTAs):
+  // reversing every other round evens out the work per CTA when the sizes fall off in plateaus.
+  const int grid = static_cast<int>(gridDim.x);
+  const int round = t / grid;
+  const int pos = (round & 1) ? round * grid + (grid - 1 - (t - round * grid)) : t;
+  if (pos >= p.num_tiles) {
+    ti.valid = false;
+    return ti;
+  }
   const int bh = p.batch * p.heads;
-  const int mrev = t / bh;
-  const int rem = t - mrev * bh;
+  const int mrev = pos / bh;
+  const int rem = pos - mrev * bh;
   ti.b = rem / p.heads;
   ti.h = rem - ti.b * p.heads;
   ti.hk = ti.h / p.group;
@@ -250,7 +259,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
 #ifdef FA2_TIMING
     int tm_tile = 0;
 #endif
-    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+    for (int t = blockIdx.x; t - static_cast<int>(blockIdx.x) < p.num_tiles; t += gridDim.x) {
       const Tile ti = get_tile(p, t);
       if (!ti.valid) continue;
       const int r_lo = ti.m0 + s * kBlockM;
@@ -292,8 +301,20 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         if (p.window_left >= 0) need_mask |= (col0 < r_hi + ti.off - p.window_left);
         bool grow;
         float alpha = 1.f;
-        if (!fancy && !need_mask) {
-          // ---- fast path: row max with 3-input max, then the O rescale decision
+        if (!fancy) {
+          // ---- fast path (also for tiles that touch a mask boundary: masked scores become -inf first):
+          // row max with 3-input max, then the O rescale decision
+          if (need_mask) {
+            int hi = ti.sk;
+            if (p.window_right >= 0) hi = min(hi, row + ti.off + p.window_right + 1);
+            int lo = 0;
+            if (p.window_left >= 0) lo = row + ti.off - p.window_left;
+            hi -= col0;
+            lo -= col0;
+#pragma unroll
+            for (int i = 0; i < kBlockN; ++i)
+              if (i < lo || i >= hi) sr[i] = __float_as_uint(-INFINITY);
+          }
           float mx0 = max3(__uint_as_float(sr[0]), __uint_as_float(sr[1]), __uint_as_float(sr[2]));
           float mx1 = max3(__uint_as_float(sr[3]), __uint_as_float(sr[4]), __uint_as_float(sr[5]));
           float mx2 = max3(__uint_as_float(sr[6]), __uint_as_float(sr[7]), __uint_as_float(sr[8]));
@@ -390,13 +411,15 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
 #ifdef FA2_TIMING
         if (tm_on) FA2_STAMP(tm_base + 3);
 #endif
-        if (!fancy && !need_mask) {
+        if (!fancy) {
           // ---- fast path: x = s * c - m with packed FMAs; kPolyPairs of every four pairs take their
           // exponential on the FMA pipe, the others on the MUFU unit; packed row-sum accumulation.
           const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2);
-          const uint64_t nm2 = pack_f32x2(-m, -m);  // m is finite here: the tile has no masked score
+          // A row that has seen no key yet has m = -inf and only -inf scores: keep x = -inf (not NaN).
+          const float neg_m = (m == -INFINITY) ? 0.f : -m;
+          const uint64_t nm2 = pack_f32x2(neg_m, neg_m);
           uint64_t acc0 = pack_f32x2(0.f, 0.f), acc1 = acc0;
-          constexpr int kPieceCols = kBlockN / kPQ;  // 32 scores -> 16 packed TMEM columns
+          constexpr int kPieceCols = kBlockN / kPQ;
 #pragma unroll
           for (int i = 0; i < kBlockN; i += 8) {
             float x[8];
@@ -452,7 +475,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
 #ifdef FA2_TIMING
         if (tm_on) FA2_STAMP(tm_base + 4);
 #endif
-        if (fancy || need_mask) {
+        if (fancy) {
 #pragma unroll
           for (int c = 0; c < kBlockN / 8; ++c) store_p_chunk(c, sr[4 * c], sr[4 * c + 1], sr[4 * c + 2], sr[4 * c + 3]);
           fence_proxy_async_smem();
@@ -550,7 +573,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         }
         return true;
       };
-      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+      for (int t = blockIdx.x; t - static_cast<int>(blockIdx.x) < p.num_tiles && ok; t += gridDim.x) {
         const Tile ti = get_tile(p, t);
         if (!ti.valid) continue;
         auto load_q = [&](int s) -> bool {
@@ -612,7 +635,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           ring_phase ^= 1;
         }
       };
-      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+      for (int t = blockIdx.x; t - static_cast<int>(blockIdx.x) < p.num_tiles && ok; t += gridDim.x) {
         const Tile ti = get_tile(p, t);
         if (!ti.valid) continue;
         const int nb = s ? ti.nb[1] : ti.nb[0], ne = s ? ti.ne[1] : ti.ne[0];
