@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     }
     for (int st = 0; st < 2; ++st) {
       mbar_init(&do_full[st], 1);
-      mbar_init(&do_empty[st], want_dq ? 2 : 1);
+      mbar_init(&do_empty[st], want_dq ? 5 : 1);  // the dV commit and, with dQ, the four drain warps
     }
     mbar_init(s_full, 1);
     mbar_init(p_full, 256);
@@ -520,13 +520,12 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     // ------------------------------------------------------------------ dQ drain
     // The whole 128 x D fp32 tile goes to registers at once so that the dP^T / dQ columns are free
     // for the next iteration right away; it then leaves through the dO stage this iteration has
-    // retired (two 16 KB pieces at a time) as cp.reduce.async.bulk adds into the accumulator.
+    // retired as cp.reduce.async.bulk adds into the accumulator.
     reg_alloc<kDrainRegs>();
     const int rt = tid - 384;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_dq = tmem + lane_addr + Cfg::kTmemDP;
     if (want_dq) {
-      uint32_t n_round = 0;
       bool ok = true;
       for (int it = 0; it < n_iter && ok; ++it) {
         const int hq = ti.hk * p.group + it / ti.n_m;
@@ -543,49 +542,42 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         tc_fence_before();
         mbar_arrive(dq_free);
         if (rt == 0 && it < 20) FA2_BSTAMP(640 + it * 4 + 1);
-        constexpr int kRounds = (D / 32 + 1) / 2;                          // two pieces per round
-        constexpr int kPiecesPerRound = (Cfg::kTileBytes >= 2 * Cfg::kPieceBytes) ? 2 : 1;
+        // Each warp drains its own 32 rows: pieces of 32 fp32 columns (4 KB) roll through the warp's share
+        // of the stage (two buffers at D = 128). Piece k is staged as soon as the reduce of piece k - kBufs
+        // has read its buffer, so the reduce engine always has a piece queued, and nothing but the warp
+        // itself has to be synchronised.
+        constexpr int kPieces = D / 32;
+        constexpr int kBufs = (Cfg::kTileBytes >= 2 * Cfg::kPieceBytes) ? 2 : 1;
+        constexpr int kWarpPiece = Cfg::kPieceBytes / 4;
+        uint8_t* warp_stage = stage + (warp & 3) * (kBufs * kWarpPiece);
 #pragma unroll
-        for (int r = 0; r < D / 32 / kPiecesPerRound; ++r) {
-          if (r > 0) {
-            // The reduces of the previous round must have read the staging pieces.
-            if (rt == 0) {
-              tma_wait_group_read<0>();
-              mbar_arrive(stage_free);
-            }
-            if (!mbar_wait(stage_free, n_round & 1, ctl, kWaitBwd + 17)) { ok = false; break; }
-            ++n_round;
+        for (int k = 0; k < kPieces; ++k) {
+          uint8_t* buf = warp_stage + (k % kBufs) * kWarpPiece;
+          if (k >= kBufs) {
+            if (lane == 0) tma_wait_group_read<kBufs - 1>();
+            __syncwarp();
           }
+          uint8_t* rowp = buf + lane * 128;
 #pragma unroll
-          for (int pc = 0; pc < kPiecesPerRound; ++pc) {
-            uint8_t* rowp = stage + pc * Cfg::kPieceBytes + rt * 128;
-            const int c0 = (r * kPiecesPerRound + pc) * 32;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-              *reinterpret_cast<uint4*>(rowp + ((c ^ (rt & 7)) << 4)) =
-                  make_uint4(acc[c0 + 4 * c], acc[c0 + 4 * c + 1], acc[c0 + 4 * c + 2], acc[c0 + 4 * c + 3]);
-          }
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(rowp + ((c ^ (lane & 7)) << 4)) =
+                make_uint4(acc[k * 32 + 4 * c], acc[k * 32 + 4 * c + 1], acc[k * 32 + 4 * c + 2], acc[k * 32 + 4 * c + 3]);
           fence_proxy_async_smem();
-          mbar_arrive(stage_full);
-          if (rt == 0) {
-            if (!mbar_wait(stage_full, (it * (D / 32 / kPiecesPerRound) + r) & 1, ctl, kWaitBwd + 18)) { ok = false; break; }
-#pragma unroll
-            for (int pc = 0; pc < kPiecesPerRound; ++pc)
-              tma_reduce_add_4d(&p.tm_dqa, stage + pc * Cfg::kPieceBytes, (r * kPiecesPerRound + pc) * 32, hq,
-                                ti.q_row0 + m0, ti.bq);
+          __syncwarp();
+          if (lane == 0) {
+            tma_reduce_add_4d(&p.tm_dqa, buf, k * 32, hq, ti.q_row0 + m0 + (warp & 3) * 32, ti.bq);
             tma_commit_group();
           }
         }
-        (void)kRounds;
         if (!ok) break;
         // Hand the stage back to the loader once the last reduces have read it.
-        if (rt == 0) {
+        if (lane == 0) {
           tma_wait_group_read<0>();
           mbar_arrive(&do_empty[st]);
-          if (it < 20) FA2_BSTAMP(640 + it * 4 + 2);
+          if (rt == 0 && it < 20) FA2_BSTAMP(640 + it * 4 + 2);
         }
       }
-      if (rt == 0) tma_wait_group<0>();
+      if (lane == 0) tma_wait_group<0>();
     }
   }
   __syncwarp();

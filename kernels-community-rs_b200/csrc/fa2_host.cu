@@ -399,7 +399,7 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
   if ((rc = make_map(&p.tm_dv, a->dv, a->dtype, 2, d, a->heads_k, rows_k, nbatch, d, hkd, rows_k * hkd, 64, 128,
                      "dv")) != FA2_OK) return rc;
   if (want_dq) {
-    if ((rc = make_map(&p.tm_dqa, a->dq_accum, 2, 4, d, a->heads, rows_q, nbatch, d, hd, rows_q * hd, 32, 128,
+    if ((rc = make_map(&p.tm_dqa, a->dq_accum, 2, 4, d, a->heads, rows_q, nbatch, d, hd, rows_q * hd, 32, 32,
                        "dq_accum")) != FA2_OK) return rc;
   } else {
     p.tm_dqa = p.tm_q;
@@ -565,7 +565,7 @@ int bwd_static_impl(const fa2_bwd_args* a, void* stream_v) {
                      "dk")) != FA2_OK) return rc;
   if ((rc = make_map(&p.tm_dv, a->dv, a->dtype, 2, d, a->heads_k, rows_k, nbatch, d, hkd, rows_k * hkd, 64, 128,
                      "dv")) != FA2_OK) return rc;
-  if ((rc = make_map(&p.tm_dqa, rt->accum, 2, 4, d, a->heads, rows_q, nbatch, d, hd, rows_q * hd, 32, 128,
+  if ((rc = make_map(&p.tm_dqa, rt->accum, 2, 4, d, a->heads, rows_q, nbatch, d, hd, rows_q * hd, 32, 32,
                      "static dq accumulator")) != FA2_OK) return rc;
   p.lse = a->lse;
   p.delta = a->delta;
