@@ -48,7 +48,7 @@ struct FwdParams {
 struct BwdParams {
   CUtensorMap tm_q, tm_k, tm_v, tm_do;  // 16-bit inputs, box (64, 1, 128, 1)
   CUtensorMap tm_dk, tm_dv;             // 16-bit outputs, box (64, 1, 128, 1)
-  CUtensorMap tm_dqa;                   // fp32 dQ accumulator, box (32, 1, 128, 1)
+  CUtensorMap tm_dqa;                   // fp32 dQ accumulator, box (32, 1, 32, 1): one drain warp's rows
   const float* lse;
   const float* delta;
   void* dk_ptr;
