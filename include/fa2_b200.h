@@ -124,6 +124,17 @@ typedef struct fa2_bwd_args {
 FA2_API int64_t fa2_bwd_workspace_bytes(const fa2_bwd_args* args);
 FA2_API int fa2_bwd(const fa2_bwd_args* args, void* stream);
 
+/* Views the kernels cannot address (base not 16-byte aligned, or an outer stride that is not a
+ * multiple of 8 elements) are copied into a packed tensor first, as prepare_attention_tensor does
+ * (flash-attn2-rs/src/host/layout.rs:80-100, kernel src/device/layout.rs:4-35). The C ABI does not
+ * allocate: the caller tests the view with fa2_layout_is_addressable() (1 = usable as it is) and, if
+ * needed, packs it into its own contiguous buffer with fa2_pack_16bit(): `shape` is [n0, n1, n2, d]
+ * (use n0 = 1 for packed [total, H, D] tensors), `outer_strides` the element strides of n0, n1, n2;
+ * the last dimension has stride 1. */
+FA2_API int fa2_layout_is_addressable(const void* ptr, const int64_t* outer_strides, int32_t n_outer);
+FA2_API int fa2_pack_16bit(const void* src, void* dst, const int64_t shape[4], const int64_t outer_strides[3],
+                           void* stream);
+
 /* Backward that allocates nothing. No counterpart in the reference crate (its host layer always
  * allocates its workspaces through the tvm-ffi environment allocator).
  *

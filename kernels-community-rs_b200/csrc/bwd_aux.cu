@@ -110,6 +110,33 @@ cudaError_t launch_bwd_preprocess(const PreprocessParams& p, cudaStream_t stream
   return cudaGetLastError();
 }
 
+// 16-bit tensor [n0, n1, n2, d] with unit last stride and arbitrary outer strides -> contiguous copy.
+// Stands in for the reference's packing kernel (flash-attn2-rs/src/device/layout.rs:4-35), which runs
+// when a view cannot be addressed by the main kernels (there: 16-byte alignment of the row starts).
+__global__ void __launch_bounds__(256) pack_rows_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst,
+                                                        int64_t total, int n1, int n2, int d, int64_t s0, int64_t s1,
+                                                        int64_t s2) {
+  const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (i >= total) return;
+  const int c = static_cast<int>(i % d);
+  int64_t r = i / d;
+  const int i2 = static_cast<int>(r % n2);
+  r /= n2;
+  const int i1 = static_cast<int>(r % n1);
+  const int64_t i0 = r / n1;
+  dst[i] = src[i0 * s0 + i1 * s1 + i2 * s2 + c];
+}
+
+cudaError_t launch_pack_rows(const void* src, void* dst, int64_t n0, int64_t n1, int64_t n2, int64_t d, int64_t s0,
+                             int64_t s1, int64_t s2, cudaStream_t stream) {
+  const int64_t total = n0 * n1 * n2 * d;
+  if (total == 0) return cudaSuccess;
+  const unsigned grid = static_cast<unsigned>((total + 255) / 256);
+  pack_rows_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), total,
+                                             static_cast<int>(n1), static_cast<int>(n2), static_cast<int>(d), s0, s1, s2);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_dq_convert(const float* src, void* dst, int64_t n, float scale, bool bf16, cudaStream_t stream) {
   const int64_t n8 = n / 8;
   if (n8 == 0) return cudaSuccess;

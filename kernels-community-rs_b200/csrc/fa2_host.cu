@@ -7,6 +7,7 @@
 
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <climits>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -617,6 +618,23 @@ int64_t fa2_bwd_workspace_bytes(const fa2_bwd_args* args) {
 }
 
 int fa2_bwd(const fa2_bwd_args* args, void* stream) { return bwd_impl(args, stream); }
+
+int fa2_layout_is_addressable(const void* ptr, const int64_t* outer_strides, int32_t n_outer) {
+  if (ptr == nullptr || reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return 0;
+  for (int i = 0; i < n_outer; ++i)
+    if (outer_strides[i] % 8 != 0 || outer_strides[i] < 0) return 0;
+  return 1;
+}
+
+int fa2_pack_16bit(const void* src, void* dst, const int64_t shape[4], const int64_t outer_strides[3], void* stream) {
+  if (src == nullptr || dst == nullptr) return fail(FA2_E_VALUE, "fa2_pack_16bit: null tensor");
+  for (int i = 0; i < 4; ++i)
+    if (shape[i] < 0 || shape[i] > INT32_MAX) return fail(FA2_E_VALUE, "fa2_pack_16bit: unsupported shape");
+  cudaError_t e = fa2::launch_pack_rows(src, dst, shape[0], shape[1], shape[2], shape[3], outer_strides[0],
+                                        outer_strides[1], outer_strides[2], static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "packing copy launch failed: %s", cudaGetErrorString(e));
+  return FA2_OK;
+}
 
 int fa2_bwd_static(const fa2_bwd_args* args, void* stream) { return bwd_static_impl(args, stream); }
 

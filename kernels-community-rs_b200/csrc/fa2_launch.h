@@ -16,6 +16,8 @@ cudaError_t launch_bwd(const BwdParams& p, int head_dim, bool bf16, int num_sms,
 cudaError_t launch_bwd_preprocess(const PreprocessParams& p, cudaStream_t stream);
 
 // dst(16-bit) = src(fp32) * scale over n elements (n a multiple of 8).
+cudaError_t launch_pack_rows(const void* src, void* dst, int64_t n0, int64_t n1, int64_t n2, int64_t d, int64_t s0,
+                             int64_t s1, int64_t s2, cudaStream_t stream);
 cudaError_t launch_dq_convert(const float* src, void* dst, int64_t n, float scale, bool bf16, cudaStream_t stream);
 
 }  // namespace fa2

@@ -102,6 +102,25 @@ bool is_contiguous(const Tensor& t) {
   return true;
 }
 
+// A view the kernels cannot address (base not 16-byte aligned or an outer stride that is not a
+// multiple of 8 elements) is packed into a fresh contiguous tensor from the environment allocator,
+// as prepare_attention_tensor does (host/layout.rs:80-100); anything else is returned as it is.
+Tensor addressable(const Tensor& t, DLDevice dev) {
+  int64_t strides[3];
+  const auto st = t.strides();
+  const auto sh = t.shape();
+  const int nd = t.ndim();
+  for (int i = 0; i < nd - 1; ++i) strides[i] = sh[i] > 1 ? st[i] : 0;  // the stride of a size-1 dimension is never used
+  if (fa2_layout_is_addressable(t.data_ptr(), strides, nd - 1)) return t;
+  int64_t shape4[4] = {1, 1, 1, 1}, outer[3] = {0, 0, 0};
+  for (int i = 0; i < nd; ++i) shape4[4 - nd + i] = sh[i];
+  for (int i = 0; i < nd - 1; ++i) outer[3 - (nd - 1) + i] = st[i];
+  std::vector<int64_t> shp(sh.begin(), sh.end());
+  Tensor packed = Tensor::FromEnvAlloc(TVMFFIEnvTensorAlloc, tvm::ffi::ShapeView(shp.data(), shp.size()), t.dtype(), dev);
+  check(fa2_pack_16bit(t.data_ptr(), packed.data_ptr(), shape4, outer, stream_of(dev)));
+  return packed;
+}
+
 void unsupported(const char* what) {
   TVM_FFI_THROW(ValueError) << what << " is not built in the sm_100a library";
 }
@@ -165,6 +184,9 @@ Any fwd_impl(const AnyView* args, int32_t n, bool lse_only) {
     TVM_FFI_THROW(ValueError) << "k and v must be on the same device as q";
   if (wl < INT32_MIN || wl > INT32_MAX || wr < INT32_MIN || wr > INT32_MAX)
     TVM_FFI_THROW(ValueError) << "window sizes must fit int32";
+  q = addressable(q, dev);
+  k = addressable(k, dev);
+  v = addressable(v, dev);
 
   Optional<Tensor> supplied;
   if (n == 10 || n == 13 || n == 14 || n == 16 || n == 18)
@@ -221,6 +243,8 @@ Any bwd_preprocess_impl(const AnyView* args, int32_t n) {
   bool same = dtype_code(out, "out") == dt && dout.device().device_id == out.device().device_id;
   for (int i = 0; same && i < 4; ++i) same = dout.shape()[i] == out.shape()[i];
   if (!same) TVM_FFI_THROW(ValueError) << "dout and out must share shape, dtype and device";
+  dout = addressable(dout, dout.device());
+  out = addressable(out, out.device());
   const int64_t b = out.shape()[0], s = out.shape()[1], h = out.shape()[2], d = out.shape()[3];
   if (b <= 0 || h <= 0 || b > 65535 || h > 65535 || s < 0 || d < 8 || d > 256 || d % 8 != 0)
     TVM_FFI_THROW(ValueError) << "unsupported backward tensor dimensions";
@@ -269,6 +293,10 @@ Any bwd_impl(const AnyView* args, int32_t n, int which) {
   for (int i = 0; ok && i < 4; ++i) ok = v.shape()[i] == k.shape()[i] && dout.shape()[i] == q.shape()[i];
   if (!ok) TVM_FFI_THROW(ValueError) << "dout must match q, and k, v must be [B, Sk, Hk, D] with q's batch and head dim";
   const DLDevice dev = q.device();
+  q = addressable(q, dev);
+  k = addressable(k, dev);
+  v = addressable(v, dev);
+  dout = addressable(dout, dev);
   const int64_t sq_pad = (sq + 127) / 128 * 128;
   auto f32_on_dev = [&](const Tensor& t) {
     return t.dtype().code == kDLFloat && t.dtype().bits == 32 && t.device().device_type == kDLCUDA &&
@@ -382,6 +410,11 @@ Any varlen_fwd_impl(const AnyView* args, int32_t n) {
     TVM_FFI_THROW(ValueError) << "cu_seqlens_q must have shape [batch + 1]";
   const int64_t batch = cuq.value().shape()[0] - 1;
 
+  for (Tensor* t : {&q, &k, &v}) {
+    check_attention_tensor(*t, "q, k, v", 3, 4);
+    dtype_code(*t, "q, k, v");
+    *t = addressable(*t, t->device());
+  }
   const Packed pq = packed_shape(q, "q"), pk = packed_shape(k, "k"), pv = packed_shape(v, "v");
   const int dt = dtype_code(q, "q");
   const DLDevice dev = q.device();
@@ -458,6 +491,11 @@ Any varlen_bwd_impl(const AnyView* args, int32_t n) {
   if (cap > 0.0) unsupported("softcap in the backward pass");
   if (cuq.ndim() != 1 || cuq.shape()[0] < 2) TVM_FFI_THROW(ValueError) << "cu_seqlens_q must have shape [batch + 1]";
   const int64_t batch = cuq.shape()[0] - 1;
+  for (Tensor* t : {&q, &k, &v, &dout, &out}) {
+    check_attention_tensor(*t, "q, k, v, dout, out", 3, 4);
+    dtype_code(*t, "q, k, v, dout, out");
+    *t = addressable(*t, t->device());
+  }
   const Packed pq = packed_shape(q, "q"), pk = packed_shape(k, "k"), pv = packed_shape(v, "v");
   const Packed pd = packed_shape(dout, "dout"), po = packed_shape(out, "out");
   const int dt = dtype_code(q, "q");

@@ -218,3 +218,28 @@ def test_error_no_larger_than_twice_a_reference_class_kernel():
     e_ours = (ours.float().cpu() - o_ref).abs().max().item()
     e_theirs = (theirs - o_ref).abs().max().item()
     assert e_ours <= 2 * e_theirs + 1e-6, (e_ours, e_theirs)
+
+
+def test_unaddressable_views_are_packed_by_the_operator_layer():
+    """Views whose base is not 16-byte aligned or whose outer strides are not multiples of 8 elements go
+    through the packing copy of the operator layer (the reference packs them as well,
+    flash-attn2-rs/src/host/layout.rs:80-100); forward and backward must match the oracle on them."""
+    import flash_attn2_b200 as fa
+    from oracle.attention_oracle import attention_backward, attention_forward
+    from tests._cases import BWD_TOL
+
+    g = torch.Generator().manual_seed(11)
+    b, s, h, d = 1, 200, 3, 128
+    big = [torch.randn(b, s, h, d + 1, generator=g).to(torch.float16) for _ in range(4)]
+    views_cpu = [t[..., 1:] for t in big]                      # base off by 2 bytes, row stride 3 * 129
+    q, k, v, do = [t.cuda()[..., 1:] for t in big]
+    assert q.data_ptr() % 16 != 0 and q.stride(1) % 8 != 0
+    out, lse, _, _ = fa.fwd(q, k, v, is_causal=True)
+    o_ref, lse_ref = attention_forward(*[t.contiguous() for t in views_cpu[:3]], causal=True)
+    _check(out, lse, o_ref, lse_ref, torch.float16)
+    dq, dk, dv, _ = fa.bwd(do, q, k, v, out, lse, is_causal=True)
+    dq_ref, dk_ref, dv_ref, _ = attention_backward(*[t.contiguous() for t in views_cpu], causal=True,
+                                                   out=out.float().cpu())
+    tol = BWD_TOL[torch.float16]
+    for got, ref in ((dq, dq_ref), (dk, dk_ref), (dv, dv_ref)):
+        torch.testing.assert_close(got.float().cpu(), ref, atol=tol["atol"], rtol=tol["rtol"])
