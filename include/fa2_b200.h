@@ -120,6 +120,12 @@ typedef struct fa2_bwd_args {
    * dQ/dK/dV kernel (not the memset / convert around it), for per-kernel timing. May be NULL. */
   void* ev_kernel_start;
   void* ev_kernel_stop;
+  /* Score transforms of the forward pass that produced `lse` (flash-attn2-rs/src/host/backward.rs:15-34
+   * takes the same two): ALiBi slopes ([H] with alibi_batch_stride 0, or [B, H] with stride H; NULL
+   * for none) and the softcap (0 for none). */
+  const float* alibi_slopes;
+  int32_t alibi_batch_stride;
+  float softcap;
 } fa2_bwd_args;
 FA2_API int64_t fa2_bwd_workspace_bytes(const fa2_bwd_args* args);
 FA2_API int fa2_bwd(const fa2_bwd_args* args, void* stream);

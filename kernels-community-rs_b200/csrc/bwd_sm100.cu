@@ -75,6 +75,12 @@ struct KvTile {
   bool valid;
 };
 
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ KvTile get_kv_tile(const BwdParams& p, int t) {
   KvTile ti;
   // Consecutive CTAs walk the key blocks of one (batch, kv head): the head's Q, dO and its fp32
@@ -388,6 +394,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         v = p.delta[ti.bq * p.delta_batch_stride + hq * p.delta_head_stride + ti.q_row0 + ti.b * p.delta_seq_pad + q];
       return v;
     };
+    const bool fancy = (p.softcap > 0.f) || (p.alibi != nullptr);
     float stat_next = n_iter > 0 ? load_stat(0) : 0.f;
     for (int it = 0; it < n_iter; ++it) {
       const int m0 = (ti.m_start + it % ti.n_m) * kBlk;
@@ -420,21 +427,57 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         if (kpos >= ti.sk) c_hi = -1;
       }
       float pr[64];
+      if (!fancy) {
 #pragma unroll
-      for (int i = 0; i < 64; i += 4) {
-        const float4 l4 = lse4[i / 4];
-        pr[i] = ex2(fmaf(__uint_as_float(sr[i]), p.scale_log2, -l4.x));
-        pr[i + 1] = ex2(fmaf(__uint_as_float(sr[i + 1]), p.scale_log2, -l4.y));
-        pr[i + 2] = ex2(fmaf(__uint_as_float(sr[i + 2]), p.scale_log2, -l4.z));
-        pr[i + 3] = ex2(fmaf(__uint_as_float(sr[i + 3]), p.scale_log2, -l4.w));
+        for (int i = 0; i < 64; i += 4) {
+          const float4 l4 = lse4[i / 4];
+          pr[i] = ex2(fmaf(__uint_as_float(sr[i]), p.scale_log2, -l4.x));
+          pr[i + 1] = ex2(fmaf(__uint_as_float(sr[i + 1]), p.scale_log2, -l4.y));
+          pr[i + 2] = ex2(fmaf(__uint_as_float(sr[i + 2]), p.scale_log2, -l4.z));
+          pr[i + 3] = ex2(fmaf(__uint_as_float(sr[i + 3]), p.scale_log2, -l4.w));
+        }
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (i < c_lo || i >= c_hi) pr[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sr[i] = pack2<BF16>(pr[2 * i], pr[2 * i + 1]);
+      } else {
+        // softcap / ALiBi: P follows the transformed scores of the forward; what goes on to dS is
+        // P times the derivative of the transform, 1 - tanh^2 (the ALiBi bias is a constant).
+        const int hq = ti.hk * p.group + it / ti.n_m;
+        const float slope = (p.alibi != nullptr) ? p.alibi[ti.b * p.alibi_batch_stride + hq] * kLog2e : 0.f;
+        const float inv_cap = (p.softcap > 0.f) ? p.scale / p.softcap : 0.f;
+        const float cap_l2 = p.softcap * kLog2e;
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) {
+          float pp[2], dd[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float raw = __uint_as_float(sr[i + e]);
+            float x, deriv = 1.f;
+            if (p.softcap > 0.f) {
+              const float t = tanh_approx(raw * inv_cap);
+              x = cap_l2 * t;
+              deriv = fmaf(-t, t, 1.f);
+            } else {
+              x = raw * p.scale_log2;
+            }
+            if (p.alibi != nullptr)
+              x += p.causal_alibi ? slope * static_cast<float>(kpos)
+                                  : -slope * fabsf(static_cast<float>(qbase + i + e + ti.off - kpos));
+            const float l = reinterpret_cast<const float*>(lse4)[i + e];
+            float pv = ex2(x - l);
+            if (need_mask && (i + e < c_lo || i + e >= c_hi)) pv = 0.f;
+            pp[e] = pv;
+            dd[e] = pv * deriv;
+          }
+          sr[i / 2] = pack2<BF16>(pp[0], pp[1]);
+          pr[i] = dd[0];
+          pr[i + 1] = dd[1];
+        }
       }
-      if (need_mask) {
-#pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (i < c_lo || i >= c_hi) pr[i] = 0.f;
-      }
-#pragma unroll
-      for (int i = 0; i < 32; ++i) sr[i] = pack2<BF16>(pr[2 * i], pr[2 * i + 1]);
       tmem_st32(t_s, sr);
       tmem_wait_st();
       tc_fence_before();
@@ -499,7 +542,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           w.w = pack2<BF16>(__uint_as_float(acc[8 * c + 6]) * mul, __uint_as_float(acc[8 * c + 7]) * mul);
           if (tma_store) {
             *reinterpret_cast<uint4*>(stage + (c / 8) * (kBlk * 128) + key_in * 128 + (((c & 7) ^ (key_in & 7)) << 4)) = w;
-          } else if (kpos < ti.sk) {
+          } else if (kpos < ti.sk && c * 8 < p.head_dim) {
             *reinterpret_cast<uint4*>(grow + c * 8) = w;
           }
         }
@@ -509,7 +552,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           if ((ct & 127) == 0 && mbar_wait(&epi_full[wg], 0, ctl, kWaitBwd + 16)) {
 #pragma unroll
             for (int a = 0; a < Cfg::kAtoms; ++a)
-              tma_store_4d(tm, stage + a * (kBlk * 128), a * 64, ti.hk, ti.k_row0 + ti.n0, ti.bq);
+              if (a * 64 < p.head_dim) tma_store_4d(tm, stage + a * (kBlk * 128), a * 64, ti.hk, ti.k_row0 + ti.n0, ti.bq);
             tma_commit_group();
             tma_wait_group<0>();
           }
@@ -565,7 +608,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_reduce_add_4d(&p.tm_dqa, buf, k * 32, hq, ti.q_row0 + m0 + (warp & 3) * 32, ti.bq);
+            if (k * 32 < p.head_dim) tma_reduce_add_4d(&p.tm_dqa, buf, k * 32, hq, ti.q_row0 + m0 + (warp & 3) * 32, ti.bq);
             tma_commit_group();
           }
         }
@@ -608,8 +651,8 @@ cudaError_t launch_one(const BwdParams& p, int num_ctas, cudaStream_t stream) {
 cudaError_t launch_bwd(const BwdParams& p, int head_dim, bool bf16, int /*num_sms*/, cudaStream_t stream) {
   const int num_ctas = p.num_nblk * p.batch * p.heads_k;
   if (num_ctas <= 0) return cudaSuccess;
-  if (head_dim == 128) return bf16 ? launch_one<128, true>(p, num_ctas, stream) : launch_one<128, false>(p, num_ctas, stream);
-  if (head_dim == 64) return bf16 ? launch_one<64, true>(p, num_ctas, stream) : launch_one<64, false>(p, num_ctas, stream);
+  if (head_dim > 64 && head_dim <= 128) return bf16 ? launch_one<128, true>(p, num_ctas, stream) : launch_one<128, false>(p, num_ctas, stream);
+  if (head_dim > 0 && head_dim <= 64) return bf16 ? launch_one<64, true>(p, num_ctas, stream) : launch_one<64, false>(p, num_ctas, stream);
   return cudaErrorInvalidValue;
 }
 

@@ -167,8 +167,7 @@ int fwd_common(const fa2_fwd_args* a, void* stream_v, bool packed) {
   const int d = a->head_dim;
   if (d > 256) return fail(FA2_E_VALUE, "head dim must be <= 256, got %d", d);
   if (d < 8 || d % 8 != 0) return fail(FA2_E_VALUE, "head_size must be a positive multiple of 8, got %d", d);
-  if (d != 64 && d != 128)
-    return fail(FA2_E_VALUE, "head dim %d is not built for sm_100a yet (64 and 128 are)", d);
+  if (d > 128) return fail(FA2_E_VALUE, "head dim %d is not built for sm_100a yet (multiples of 8 up to 128 are)", d);
   if (a->heads_k <= 0 || a->heads % a->heads_k != 0)
     return fail(FA2_E_VALUE, "num_heads (%d) must be a multiple of num_heads_k (%d)", a->heads, a->heads_k);
   if (a->batch <= 0 || a->heads <= 0 || a->batch > 65535 || a->heads > 65535)
@@ -274,6 +273,7 @@ int fwd_common(const fa2_fwd_args* a, void* stream_v, bool packed) {
   p.softcap = a->softcap > 0.f ? a->softcap : 0.f;
   p.status = rt->status;
 
+  p.head_dim = d;
   cudaError_t e = fa2::launch_fwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream);
   if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "forward launch failed: %s", cudaGetErrorString(e));
   return FA2_OK;
@@ -337,7 +337,8 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
   const bool packed = a->cu_seqlens_q != nullptr;
   const int d = a->head_dim;
   if (d > 256 || d < 8 || d % 8 != 0) return fail(FA2_E_VALUE, "unsupported backward tensor dimensions");
-  if (d != 64 && d != 128) return fail(FA2_E_VALUE, "head dim %d is not built for sm_100a yet (64 and 128 are)", d);
+  if (d < 8 || d % 8 != 0 || d > 128)
+    return fail(FA2_E_VALUE, "head dim %d is not built for sm_100a yet (multiples of 8 up to 128 are)", d);
   if (a->heads_k <= 0 || a->heads % a->heads_k != 0)
     return fail(FA2_E_VALUE, "num_heads (%d) must be a multiple of num_heads_k (%d)", a->heads, a->heads_k);
   if (a->batch <= 0 || a->heads <= 0 || a->batch > 65535 || a->heads > 65535 || a->seqlen_q < 0 || a->seqlen_k < 0)
@@ -439,6 +440,10 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
   p.window_left = w.left;
   p.window_right = w.right;
   p.which = a->which;
+  p.alibi = a->alibi_slopes;
+  p.alibi_batch_stride = a->alibi_batch_stride;
+  p.causal_alibi = w.causal_alibi;
+  p.softcap = a->softcap > 0.f ? a->softcap : 0.f;
   p.scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.status = rt->status;
@@ -447,6 +452,7 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
   if (want_dq && (e = cudaMemsetAsync(a->dq_accum, 0, n_dq * 4, stream)) != cudaSuccess)
     return fail(FA2_E_RUNTIME, "memset failed: %s", cudaGetErrorString(e));
   if (a->ev_kernel_start != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_kernel_start), stream);
+  p.head_dim = d;
   e = fa2::launch_bwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream);
   if (a->ev_kernel_stop != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_kernel_stop), stream);
   if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "backward launch failed: %s", cudaGetErrorString(e));
@@ -521,7 +527,8 @@ int bwd_static_impl(const fa2_bwd_args* a, void* stream_v) {
   if (a->cu_seqlens_q != nullptr || a->cu_seqlens_k != nullptr)
     return fail(FA2_E_VALUE, "fa2_bwd_static takes dense [B, S, H, D] tensors only");
   const int d = a->head_dim;
-  if (d != 64 && d != 128) return fail(FA2_E_VALUE, "head dim %d is not built for sm_100a (64 and 128 are)", d);
+  if (d < 8 || d % 8 != 0 || d > 128)
+    return fail(FA2_E_VALUE, "head dim %d is not built for sm_100a (multiples of 8 up to 128 are)", d);
   if (a->heads_k <= 0 || a->heads % a->heads_k != 0)
     return fail(FA2_E_VALUE, "num_heads (%d) must be a multiple of num_heads_k (%d)", a->heads, a->heads_k);
   if (a->batch <= 0 || a->heads <= 0 || a->batch > 65535 || a->heads > 65535 || a->seqlen_q <= 0 || a->seqlen_k <= 0)
@@ -591,6 +598,10 @@ int bwd_static_impl(const fa2_bwd_args* a, void* stream_v) {
   p.window_left = w.left;
   p.window_right = w.right;
   p.which = 3;
+  p.alibi = a->alibi_slopes;
+  p.alibi_batch_stride = a->alibi_batch_stride;
+  p.causal_alibi = w.causal_alibi;
+  p.softcap = a->softcap > 0.f ? a->softcap : 0.f;
   p.scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.status = rt->status;
@@ -599,6 +610,7 @@ int bwd_static_impl(const fa2_bwd_args* a, void* stream_v) {
   // The array keeps whatever the previous call left: the part this call adds into starts at zero.
   cudaError_t e = cudaMemsetAsync(rt->accum, 0, static_cast<size_t>(n_dq) * 4, stream);
   if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "memset failed: %s", cudaGetErrorString(e));
+  p.head_dim = d;
   if ((e = fa2::launch_bwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream)) != cudaSuccess)
     return fail(FA2_E_RUNTIME, "backward launch failed: %s", cudaGetErrorString(e));
   if ((e = fa2::launch_dq_convert(rt->accum, a->dq, n_dq, a->softmax_scale, a->dtype == FA2_BF16, stream)) != cudaSuccess)

@@ -43,6 +43,7 @@ struct FwdParams {
   float scale_log2;                    // scale * log2(e)
   float softcap;                       // 0 = off
   int* status;                         // device status word (0 = ok)
+  int head_dim;                         // real head dim (<= the kernel's D; columns beyond it are padding)
 };
 
 struct BwdParams {
@@ -66,6 +67,12 @@ struct BwdParams {
   float scale, scale_log2;
   int* status;
   int* tile_counter;                    // device work counter of this launch, zero at launch
+  // Score transforms of the forward that the gradients have to follow (null / 0 when unused).
+  const float* alibi;                   // [heads] or [batch, heads] slopes
+  int alibi_batch_stride;
+  int causal_alibi;                     // bias = slope * key index instead of -slope * |distance|
+  float softcap;                        // scores = softcap * tanh(raw * scale / softcap)
+  int head_dim;                         // real head dim (<= the kernel's D; columns beyond it are padding)
 };
 
 struct PreprocessParams {

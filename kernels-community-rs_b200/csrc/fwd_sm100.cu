@@ -520,7 +520,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             // chunk c lives in swizzle atom c / 8, at position (c % 8) ^ (row % 8) of the row's 128-byte line
             *reinterpret_cast<uint4*>(stage_smem + (c / 8) * (kBlockM * 128) + row_in * 128 +
                                       (((c & 7) ^ (row_in & 7)) << 4)) = w;
-          } else if (row < ti.sq) {
+          } else if (row < ti.sq && c * 8 < p.head_dim) {
             *reinterpret_cast<uint4*>(orow + c * 8) = w;
           }
         }
@@ -531,7 +531,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             if (!mbar_wait(&epi_full[s], n_store & 1, ctl, kWaitEpiFinal)) break;
 #pragma unroll
             for (int a = 0; a < Cfg::kAtoms; ++a)
-              tma_store_4d(&p.tm_o, stage_smem + a * (kBlockM * 128), a * 64, ti.h, ti.q_row0 + r_lo, ti.bq);
+              if (a * 64 < p.head_dim)
+                tma_store_4d(&p.tm_o, stage_smem + a * (kBlockM * 128), a * 64, ti.h, ti.q_row0 + r_lo, ti.bq);
             tma_commit_group();
           }
           ++n_store;
@@ -541,7 +542,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         if (row < ti.sq) {
           // No key is visible to this stage: O = 0.
 #pragma unroll
-          for (int q = 0; q < D / 8; ++q) *reinterpret_cast<uint4*>(orow + q * 8) = make_uint4(0, 0, 0, 0);
+          for (int q = 0; q < D / 8; ++q)
+            if (q * 8 < p.head_dim) *reinterpret_cast<uint4*>(orow + q * 8) = make_uint4(0, 0, 0, 0);
         }
       }
 #ifdef FA2_TIMING
@@ -737,8 +739,9 @@ cudaError_t launch_one(const FwdParams& p, int num_sms, cudaStream_t stream) {
 
 cudaError_t launch_fwd(const FwdParams& p, int head_dim, bool bf16, int num_sms, cudaStream_t stream) {
   if (p.num_tiles <= 0) return cudaSuccess;
-  if (head_dim == 128) return bf16 ? launch_one<128, true>(p, num_sms, stream) : launch_one<128, false>(p, num_sms, stream);
-  if (head_dim == 64) return bf16 ? launch_one<64, true>(p, num_sms, stream) : launch_one<64, false>(p, num_sms, stream);
+  // Head dims below the kernel's D ride on TMA: loads past the real head dim read zeros, stores are clipped.
+  if (head_dim > 64 && head_dim <= 128) return bf16 ? launch_one<128, true>(p, num_sms, stream) : launch_one<128, false>(p, num_sms, stream);
+  if (head_dim > 0 && head_dim <= 64) return bf16 ? launch_one<64, true>(p, num_sms, stream) : launch_one<64, false>(p, num_sms, stream);
   return cudaErrorInvalidValue;
 }
 

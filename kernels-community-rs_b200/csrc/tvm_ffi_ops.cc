@@ -280,8 +280,6 @@ Any bwd_impl(const AnyView* args, int32_t n, int which) {
   const int64_t wl = arg<int64_t>(args, 9, "window_size_left"), wr = arg<int64_t>(args, 10, "window_size_right");
   const double softcap = arg<double>(args, 11, "softcap");
   check_dropout_zero(arg<double>(args, 12, "p_dropout"));
-  if (alibi.has_value()) unsupported("ALiBi in the backward pass");
-  if (softcap > 0.0) unsupported("softcap in the backward pass");
   for (auto [t, name] : {std::pair<const Tensor&, const char*>{q, "q"}, {k, "k"}, {v, "v"}, {dout, "dout"}})
     check_attention_tensor(t, name, 4, 4);
   const int dt = dtype_code(q, "q");
@@ -328,6 +326,8 @@ Any bwd_impl(const AnyView* args, int32_t n, int which) {
   fill_strides(k, a.k_stride);
   fill_strides(v, a.v_stride);
   fill_strides(dout, a.do_stride);
+  a.alibi_slopes = alibi_ptr(alibi, b, h, dev, &a.alibi_batch_stride);
+  a.softcap = static_cast<float>(softcap);
   a.softmax_scale = static_cast<float>(scale_opt.has_value() ? scale_opt.value() : 1.0 / std::sqrt(static_cast<double>(d)));
   a.causal = causal;
   a.window_left = static_cast<int32_t>(wl);
@@ -487,8 +487,6 @@ Any varlen_bwd_impl(const AnyView* args, int32_t n) {
   const double cap = arg<double>(args, 13, "cap");
   check_dropout_zero(arg<double>(args, 14, "dropout"));
   const int64_t max_q = arg<int64_t>(args, 16, "max_q"), max_k = arg<int64_t>(args, 17, "max_k");
-  if (alibi.has_value()) unsupported("ALiBi in the backward pass");
-  if (cap > 0.0) unsupported("softcap in the backward pass");
   if (cuq.ndim() != 1 || cuq.shape()[0] < 2) TVM_FFI_THROW(ValueError) << "cu_seqlens_q must have shape [batch + 1]";
   const int64_t batch = cuq.shape()[0] - 1;
   for (Tensor* t : {&q, &k, &v, &dout, &out}) {
@@ -554,6 +552,8 @@ Any varlen_bwd_impl(const AnyView* args, int32_t n) {
   a.heads = static_cast<int32_t>(h);
   a.heads_k = static_cast<int32_t>(hk);
   a.head_dim = static_cast<int32_t>(d);
+  a.alibi_slopes = alibi_ptr(alibi, batch, h, dev, &a.alibi_batch_stride);
+  a.softcap = static_cast<float>(cap);
   a.q_stride[1] = pq.row_stride;
   a.q_stride[2] = pq.head_stride;
   a.k_stride[1] = pk.row_stride;

@@ -54,6 +54,7 @@ class BwdArgs(C.Structure):
         ("cu_seqlens_q", C.c_void_p), ("cu_seqlens_k", C.c_void_p),
         ("total_q", C.c_int32), ("total_k", C.c_int32),
         ("ev_kernel_start", C.c_void_p), ("ev_kernel_stop", C.c_void_p),
+        ("alibi_slopes", C.c_void_p), ("alibi_batch_stride", C.c_int32), ("softcap", C.c_float),
     ]
 
 

@@ -171,7 +171,7 @@ def bwd_preprocess(dout, out, *, cu_seqlens_q=None, max_seqlen_q=None):
 
 def bwd(q, k, v, dout, lse, delta, *, softmax_scale=None, causal=False, window_left=-1, window_right=-1,
         which=3, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=None, max_seqlen_k=None, dq_accum=None,
-        kernel_events=None):
+        kernel_events=None, alibi_slopes=None, softcap=0.0):
     """dQ, dK, dV (input dtype, contiguous). `which`: bit 0 = dQ, bit 1 = dK and dV.
 
     `kernel_events`: optional pair of torch.cuda.Event recorded around the main kernel only."""
@@ -217,6 +217,17 @@ def bwd(q, k, v, dout, lse, delta, *, softmax_scale=None, causal=False, window_l
     a.which = int(which)
     if kernel_events is not None:
         a.ev_kernel_start, a.ev_kernel_stop = kernel_events[0].cuda_event, kernel_events[1].cuda_event
+    if alibi_slopes is not None:
+        if alibi_slopes.dtype != torch.float32 or not alibi_slopes.is_contiguous() or not alibi_slopes.is_cuda:
+            raise ValueError("alibi_slopes must be a contiguous float32 CUDA tensor")
+        if tuple(alibi_slopes.shape) == (h,):
+            a.alibi_batch_stride = 0
+        elif tuple(alibi_slopes.shape) == (b, h):
+            a.alibi_batch_stride = h
+        else:
+            raise ValueError("alibi_slopes must be [H] or [B, H]")
+        a.alibi_slopes = alibi_slopes.data_ptr()
+    a.softcap = float(softcap)
     need = lib.fa2_bwd_workspace_bytes(C.byref(a))
     if need > 0:
         if dq_accum is None:

@@ -161,3 +161,76 @@ def test_config3_full_size_slices_and_properties():
     torch.testing.assert_close(dv2.float(), dv.float() * 2, atol=2e-2, rtol=2e-2)
     torch.testing.assert_close(dk2.float(), dk.float() * 2, atol=2e-2, rtol=2e-2)
     torch.testing.assert_close(dq2.float(), dq.float() * 2, atol=2e-2, rtol=2e-2)
+
+
+FANCY_CASES = [
+    ("softcap30-causal", (1, 4, 4, 256, 256, 128), dict(causal=True, softcap=30.0), False),
+    ("alibi-causal-gqa", (2, 4, 2, 256, 256, 128), dict(causal=True), True),
+    ("alibi-full-odd", (1, 4, 4, 200, 333, 128), {}, True),
+    ("alibi-softcap-window", (1, 4, 4, 256, 256, 64), dict(window_left=64, window_right=32, softcap=20.0), True),
+]
+
+
+@pytest.mark.parametrize("name,shape,opt,use_alibi", FANCY_CASES, ids=[c[0] for c in FANCY_CASES])
+def test_backward_follows_softcap_and_alibi(name, shape, opt, use_alibi):
+    """The reference's backward operators take alibi_slopes and softcap like its forward
+    (flash-attn2-rs/src/host/backward.rs:15-34): the gradients must follow the transformed scores."""
+    from flash_attn2_b200 import cabi_ops as ops
+    from oracle.attention_oracle import attention_backward
+
+    dtype = torch.float16
+    b, h, hk, sq, sk, d = shape
+    q, k, v, do = make_qkv(7, b, h, hk, sq, sk, d, dtype, with_do=True)
+    slopes = (torch.arange(1, h + 1, dtype=torch.float32) * 0.05) if use_alibi else None
+    sl_gpu = None if slopes is None else slopes.cuda()
+    qc, kc, vc, doc = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    out, lse = ops.fwd(qc, kc, vc, alibi_slopes=sl_gpu, **opt)
+    delta = ops.bwd_preprocess(doc, out)
+    dq, dk, dv = ops.bwd(qc, kc, vc, doc, lse, delta, alibi_slopes=sl_gpu, **opt)
+    assert ops.device_status() == 0
+    dq_ref, dk_ref, dv_ref, _ = attention_backward(q, k, v, do, out=out.float().cpu(), alibi_slopes=slopes, **opt)
+    _close(dq, dq_ref, dtype, "dq")
+    _close(dk, dk_ref, dtype, "dk")
+    _close(dv, dv_ref, dtype, "dv")
+
+
+def test_backward_softcap_alibi_through_tvm_ffi_ops():
+    import flash_attn2_b200 as fa
+    from oracle.attention_oracle import attention_backward
+
+    q, k, v, do = make_qkv(8, 1, 4, 2, 256, 256, 128, torch.bfloat16, with_do=True)
+    slopes = torch.tensor([0.1, 0.2, 0.3, 0.4])
+    qc, kc, vc, doc = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    out, lse, _, _ = fa.fwd(qc, kc, vc, alibi_slopes=slopes.cuda(), is_causal=True, softcap=25.0)
+    dq, dk, dv, _ = fa.bwd(doc, qc, kc, vc, out, lse, alibi_slopes=slopes.cuda(), is_causal=True, softcap=25.0)
+    dq_ref, dk_ref, dv_ref, _ = attention_backward(q, k, v, do, causal=True, out=out.float().cpu(), alibi_slopes=slopes,
+                                                   softcap=25.0)
+    _close(dq, dq_ref, torch.bfloat16, "dq")
+    _close(dk, dk_ref, torch.bfloat16, "dk")
+    _close(dv, dv_ref, torch.bfloat16, "dv")
+
+
+@pytest.mark.parametrize("d", [32, 80, 96])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["f16", "bf16"])
+def test_forward_and_backward_other_head_dims(d, dtype):
+    """Head dims that are multiples of 8 below the kernels' 64 / 128 (the reference buckets 32..256,
+    flash-attn2-rs/src/host/tiles.rs:3-127): loads past the real head dim read zeros, stores are clipped."""
+    from flash_attn2_b200 import cabi_ops as ops
+    from oracle.attention_oracle import attention_backward, attention_forward
+    from tests._cases import FWD_TOL
+
+    q, k, v, do = make_qkv(9, 2, 4, 2, 200, 333, d, dtype, with_do=True)
+    qc, kc, vc, doc = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    out, lse = ops.fwd(qc, kc, vc, causal=True)
+    o_ref, lse_ref = attention_forward(q, k, v, causal=True)
+    tol = FWD_TOL[dtype]
+    torch.testing.assert_close(out.float().cpu(), o_ref, atol=tol["atol"], rtol=tol["rtol"])
+    torch.testing.assert_close(lse.cpu(), lse_ref, atol=tol["lse"], rtol=0)
+    delta = ops.bwd_preprocess(doc, out)
+    dq, dk, dv = ops.bwd(qc, kc, vc, doc, lse, delta, causal=True)
+    assert ops.device_status() == 0
+    dq_ref, dk_ref, dv_ref, delta_ref = attention_backward(q, k, v, do, causal=True, out=out.float().cpu())
+    torch.testing.assert_close(delta.cpu(), delta_ref, atol=2e-5, rtol=1e-5)
+    _close(dq, dq_ref, dtype, "dq")
+    _close(dk, dk_ref, dtype, "dk")
+    _close(dv, dv_ref, dtype, "dv")

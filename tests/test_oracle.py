@@ -68,3 +68,22 @@ def test_oracle_empty_rows_and_varlen_layout():
     ref, ref_l = attention_forward(qp[5:12].unsqueeze(0), kp[5:12].unsqueeze(0), vp[5:12].unsqueeze(0), causal=True)
     torch.testing.assert_close(o2[5:12], ref[0])
     torch.testing.assert_close(l2[:, 5:12], ref_l[0])
+
+
+def test_backward_formulas_with_softcap_and_alibi_match_autograd():
+    """The explicit backward (P * (dP - delta) times the derivative of the softcap) against autograd
+    through the oracle's own forward, which the golden vectors pin."""
+    from oracle.attention_oracle import attention_backward, attention_forward
+
+    g = torch.Generator().manual_seed(5)
+    q, k, v, do = [torch.randn(1, 37, 4, 16, generator=g) for _ in range(4)]
+    k, v = k[:, :, :2].contiguous(), v[:, :, :2].contiguous()
+    slopes = torch.tensor([0.1, 0.2, 0.3, 0.4])
+    for opt in (dict(causal=True, softcap=5.0), dict(softcap=3.0, window_left=8, window_right=4), dict(causal=True)):
+        qa, ka, va = [t.clone().requires_grad_() for t in (q, k, v)]
+        out, _ = attention_forward(qa, ka, va, alibi_slopes=slopes, **opt)
+        out.backward(do)
+        dq, dk, dv, _ = attention_backward(q, k, v, do, alibi_slopes=slopes, **opt)
+        torch.testing.assert_close(dq, qa.grad, atol=1e-5, rtol=1e-4)
+        torch.testing.assert_close(dk, ka.grad, atol=1e-5, rtol=1e-4)
+        torch.testing.assert_close(dv, va.grad, atol=1e-5, rtol=1e-4)

@@ -136,3 +136,32 @@ def test_config4_full_size():
     a, b = int(cu[i]), int(cu[i + 1])
     dense, dense_lse = ops.fwd(qc[a:b].unsqueeze(0), kc[a:b].unsqueeze(0), vc[a:b].unsqueeze(0), causal=True)
     assert torch.equal(dense[0], out[a:b]) and torch.equal(dense_lse[0], lse[:, a:b])
+
+
+def test_varlen_other_head_dim_ragged():
+    """Packed, ragged tiles take the predicated store paths: they must stop at the real head dim."""
+    from flash_attn2_b200 import cabi_ops as ops
+    from oracle.attention_oracle import varlen_backward, varlen_forward
+
+    lq = [130, 7, 200]
+    d = 96
+    g = torch.Generator().manual_seed(12)
+    q = torch.randn(sum(lq), 4, d, generator=g).to(torch.bfloat16)
+    k = torch.randn(sum(lq), 2, d, generator=g).to(torch.bfloat16)
+    v = torch.randn(sum(lq), 2, d, generator=g).to(torch.bfloat16)
+    do = torch.randn(sum(lq), 4, d, generator=g).to(torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(lq).cumsum(0)), dtype=torch.int32)
+    qc, kc, vc, doc, cc = q.cuda(), k.cuda(), v.cuda(), do.cuda(), cu.cuda()
+    guard = torch.full((sum(lq) + 1, 4, d), 7.0, dtype=torch.bfloat16, device="cuda")  # catches writes past a row
+    out, lse = ops.varlen_fwd(qc, kc, vc, cc, cc, max(lq), max(lq), causal=True)
+    o_ref, lse_ref = varlen_forward(q, k, v, cu, cu, causal=True)
+    _fwd_close(out, lse, o_ref, lse_ref, torch.bfloat16)
+    delta = ops.bwd_preprocess(doc, out, cu_seqlens_q=cc, max_seqlen_q=max(lq))
+    dq, dk, dv = ops.bwd(qc, kc, vc, doc, lse, delta, cu_seqlens_q=cc, cu_seqlens_k=cc, max_seqlen_q=max(lq),
+                         max_seqlen_k=max(lq), causal=True)
+    assert ops.device_status() == 0
+    dq_ref, dk_ref, dv_ref, _ = varlen_backward(q, k, v, do, cu, cu, out=out.float().cpu(), lse=lse.cpu(), causal=True)
+    tol = BWD_TOL[torch.bfloat16]
+    for got, ref in ((dq, dq_ref), (dk, dk_ref), (dv, dv_ref)):
+        torch.testing.assert_close(got.float().cpu(), ref, atol=tol["atol"], rtol=tol["rtol"])
+    assert (guard == 7.0).all()
