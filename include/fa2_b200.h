@@ -91,6 +91,11 @@ FA2_API int fa2_bwd_preprocess(const fa2_bwd_preprocess_args* args, void* stream
 /* Backward: dQ, dK, dV from Q, K, V, dO, LSE and delta. dQ is accumulated in fp32 in
  * `dq_accum` (fa2_bwd_workspace_bytes() bytes, 16-byte aligned, need not be cleared) and
  * converted to the 16-bit dQ at the end. `which` selects outputs: bit 0 = dQ, bit 1 = dK and dV.
+ * The workspace is the accumulator (B*Sq*H*D floats, rounded up to 256 bytes) followed by one 32-bit
+ * turn counter per 32 query rows of every (batch, head). With them a dQ-only call (which = 1, the
+ * deterministic bwd_dq of the reference) adds the key blocks' contributions in ascending order, so dQ
+ * is bit-reproducible; a workspace that only holds the accumulator is accepted too (arrival order).
+ * dK and dV never use atomics and are always bit-reproducible.
  * Replaces backward_component + the `backward` and `backward_kv` kernels
  * (flash-attn2-rs/src/host/backward.rs:14-566, src/device/backward/dq.rs:12-302,438-576,
  *  src/device/backward/dkv.rs:15-266,865-1012). */

@@ -81,6 +81,17 @@ __device__ __forceinline__ float tanh_approx(float x) {
   return y;
 }
 
+// Query blocks [m_start, m_start + n_m) whose rows can see a key of [n0, n0 + 127].
+__device__ __forceinline__ void q_block_range(const BwdParams& p, int sq, int sk, int n0, int& m_start, int& n_m) {
+  int q_lo = 0, q_hi = sq;  // [q_lo, q_hi)
+  const int off = sk - sq;
+  const int n_last = min(n0 + kBlk - 1, sk - 1);
+  if (p.window_right >= 0) q_lo = max(0, n0 - off - p.window_right);
+  if (p.window_left >= 0) q_hi = min(sq, n_last - off + p.window_left + 1);
+  m_start = q_lo / kBlk;
+  n_m = (q_hi > q_lo) ? ((q_hi + kBlk - 1) / kBlk - m_start) : 0;
+}
+
 __device__ __forceinline__ KvTile get_kv_tile(const BwdParams& p, int t) {
   KvTile ti;
   // Consecutive CTAs walk the key blocks of one (batch, kv head): the head's Q, dO and its fp32
@@ -108,13 +119,7 @@ __device__ __forceinline__ KvTile get_kv_tile(const BwdParams& p, int t) {
   }
   ti.off = ti.sk - ti.sq;
   ti.valid = ti.n0 < ti.sk;
-  // Query rows that can see a key of [n0, n0 + 127].
-  int q_lo = 0, q_hi = ti.sq;  // [q_lo, q_hi)
-  const int n_last = min(ti.n0 + kBlk - 1, ti.sk - 1);
-  if (p.window_right >= 0) q_lo = max(0, ti.n0 - ti.off - p.window_right);
-  if (p.window_left >= 0) q_hi = min(ti.sq, n_last - ti.off + p.window_left + 1);
-  ti.m_start = q_lo / kBlk;
-  ti.n_m = (q_hi > q_lo) ? ((q_hi + kBlk - 1) / kBlk - ti.m_start) : 0;
+  q_block_range(p, ti.sq, ti.sk, ti.n0, ti.m_start, ti.n_m);
   ti.n_iter = ti.n_m * p.group;
   return ti;
 }
@@ -593,6 +598,42 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         constexpr int kBufs = (Cfg::kTileBytes >= 2 * Cfg::kPieceBytes) ? 2 : 1;
         constexpr int kWarpPiece = Cfg::kPieceBytes / 4;
         uint8_t* warp_stage = stage + (warp & 3) * (kBufs * kWarpPiece);
+        int* turn = nullptr;
+        if (p.dq_turn != nullptr) {
+          // Ordered mode: this key block's rank among the key blocks that add into these rows (they form
+          // a contiguous range, and lower key blocks are lower CTAs of the grid, dispatched no later than
+          // this one), then a bounded wait for the slab's counter to reach it.
+          const int mq = m0 / kBlk;
+          int rank = 0;
+          for (int nb = 0; nb < ti.n0 / kBlk; nb += 32) {
+            const int n = nb + lane;
+            bool covers = false;
+            if (n < ti.n0 / kBlk) {
+              int ms, nm;
+              q_block_range(p, ti.sq, ti.sk, n * kBlk, ms, nm);
+              covers = (mq >= ms) && (mq < ms + nm);
+            }
+            rank += __popc(__ballot_sync(0xffffffffu, covers));
+          }
+          turn = p.dq_turn + ((static_cast<int64_t>(ti.b) * p.heads + hq) * p.num_mblk_q + mq) * 4 + (warp & 3);
+          if (lane == 0) {
+            const long long t0 = clock64();
+            while (*reinterpret_cast<volatile int*>(turn) != rank) {
+              __nanosleep(200);
+              if (*abort_flag || clock64() - t0 > FA2_WAIT_LIMIT_CYCLES) {
+                if (!*abort_flag) {
+                  *abort_flag = 1;
+                  if (p.status != nullptr) atomicCAS(p.status, 0, kWaitBwd + 19);
+                }
+                ok = false;
+                break;
+              }
+            }
+            __threadfence();
+          }
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) break;
+        }
 #pragma unroll
         for (int k = 0; k < kPieces; ++k) {
           uint8_t* buf = warp_stage + (k % kBufs) * kWarpPiece;
@@ -618,6 +659,13 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           tma_wait_group_read<0>();
           mbar_arrive(&do_empty[st]);
           if (rt == 0 && it < 20) FA2_BSTAMP(640 + it * 4 + 2);
+          if (turn != nullptr) {
+            // The adds have to be in memory before the next key block may start on these rows.
+            tma_wait_group<0>();
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            __threadfence();
+            atomicAdd(turn, 1);
+          }
         }
       }
       if (lane == 0) tma_wait_group<0>();

@@ -331,6 +331,16 @@ int64_t bwd_rows(const fa2_bwd_args* a) {
                                     : static_cast<int64_t>(a->batch) * a->seqlen_q;
 }
 
+// Bytes of the fp32 dQ accumulator, rounded so that what follows it is 256-byte aligned.
+int64_t bwd_accum_bytes(const fa2_bwd_args* a) {
+  return (bwd_rows(a) * a->heads * a->head_dim * 4 + 255) / 256 * 256;
+}
+
+// One counter per (batch, head, 128-row query block, 32-row slab of a drain warp).
+int64_t bwd_turn_counters(const fa2_bwd_args* a) {
+  return static_cast<int64_t>(a->batch) * a->heads * ((a->seqlen_q + 127) / 128) * 4;
+}
+
 int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
   if (a == nullptr) return fail(FA2_E_VALUE, "args is null");
   if (a->dtype != FA2_F16 && a->dtype != FA2_BF16) return fail(FA2_E_TYPE, "q, k, v must be float16 or bfloat16");
@@ -449,7 +459,14 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
   p.status = rt->status;
   p.tile_counter = next_counter(rt->status, stream);
 
-  if (want_dq && (e = cudaMemsetAsync(a->dq_accum, 0, n_dq * 4, stream)) != cudaSuccess)
+  // A dQ-only call (the deterministic pair bwd_dq + bwd_dkv of the reference, whose dQ kernel sums in
+  // registers in key order) accumulates in ascending key-block order when the workspace holds the
+  // turn counters; otherwise, and in the combined call, the adds land in arrival order.
+  const int64_t acc_bytes = bwd_accum_bytes(a), n_turn = bwd_turn_counters(a);
+  const bool ordered = a->which == 1 && a->dq_accum_bytes >= acc_bytes + n_turn * 4;
+  p.dq_turn = ordered ? reinterpret_cast<int*>(static_cast<char*>(a->dq_accum) + acc_bytes) : nullptr;
+  p.num_mblk_q = (a->seqlen_q + 127) / 128;
+  if (want_dq && (e = cudaMemsetAsync(a->dq_accum, 0, ordered ? acc_bytes + n_turn * 4 : n_dq * 4, stream)) != cudaSuccess)
     return fail(FA2_E_RUNTIME, "memset failed: %s", cudaGetErrorString(e));
   if (a->ev_kernel_start != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_kernel_start), stream);
   p.head_dim = d;
@@ -598,6 +615,8 @@ int bwd_static_impl(const fa2_bwd_args* a, void* stream_v) {
   p.window_left = w.left;
   p.window_right = w.right;
   p.which = 3;
+  p.dq_turn = nullptr;
+  p.num_mblk_q = (a->seqlen_q + 127) / 128;
   p.alibi = a->alibi_slopes;
   p.alibi_batch_stride = a->alibi_batch_stride;
   p.causal_alibi = w.causal_alibi;
@@ -626,7 +645,9 @@ int fa2_bwd_preprocess(const fa2_bwd_preprocess_args* args, void* stream) { retu
 
 int64_t fa2_bwd_workspace_bytes(const fa2_bwd_args* args) {
   if (args == nullptr || (args->which & 1) == 0) return 0;
-  return bwd_rows(args) * args->heads * args->head_dim * 4;
+  // The fp32 accumulator, then (used by dQ-only calls) one turn counter per 32 query rows of every
+  // (batch, head) for the ordered accumulation.
+  return bwd_accum_bytes(args) + bwd_turn_counters(args) * 4;
 }
 
 int fa2_bwd(const fa2_bwd_args* args, void* stream) { return bwd_impl(args, stream); }
