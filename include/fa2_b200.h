@@ -93,7 +93,7 @@ FA2_API int fa2_bwd_preprocess(const fa2_bwd_preprocess_args* args, void* stream
  * converted to the 16-bit dQ at the end. `which` selects outputs: bit 0 = dQ, bit 1 = dK and dV.
  * The workspace is the accumulator (B*Sq*H*D floats, rounded up to 256 bytes) followed by one 32-bit
  * turn counter per 32 query rows of every (batch, head). With them a dQ-only call (which = 1, the
- * deterministic bwd_dq of the reference) adds the key blocks' contributions in ascending order, so dQ
+ * deterministic bwd_dq of the reference) adds the key blocks' contributions in a fixed order, so dQ
  * is bit-reproducible; a workspace that only holds the accumulator is accepted too (arrival order).
  * dK and dV never use atomics and are always bit-reproducible.
  * Replaces backward_component + the `backward` and `backward_kv` kernels

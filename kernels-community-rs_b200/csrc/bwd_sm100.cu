@@ -600,15 +600,17 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         uint8_t* warp_stage = stage + (warp & 3) * (kBufs * kWarpPiece);
         int* turn = nullptr;
         if (p.dq_turn != nullptr) {
-          // Ordered mode: this key block's rank among the key blocks that add into these rows (they form
-          // a contiguous range, and lower key blocks are lower CTAs of the grid, dispatched no later than
-          // this one), then a bounded wait for the slab's counter to reach it.
+          // Ordered mode: the key blocks that add into these rows take their turns in descending order,
+          // which is the order in which they get there under a causal or sliding-window mask (a higher key
+          // block starts at a later query block). This block's turn is the number of higher key blocks
+          // that cover the rows; a bounded wait for the slab's counter to reach it follows. The CTAs of
+          // one head are adjacent in the grid, so the blocks waited for are resident or next in line.
           const int mq = m0 / kBlk;
           int rank = 0;
-          for (int nb = 0; nb < ti.n0 / kBlk; nb += 32) {
+          for (int nb = ti.n0 / kBlk + 1; nb < p.num_nblk; nb += 32) {
             const int n = nb + lane;
             bool covers = false;
-            if (n < ti.n0 / kBlk) {
+            if (n < p.num_nblk && n * kBlk < ti.sk) {
               int ms, nm;
               q_block_range(p, ti.sq, ti.sk, n * kBlk, ms, nm);
               covers = (mq >= ms) && (mq < ms + nm);

@@ -460,7 +460,7 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
   p.tile_counter = next_counter(rt->status, stream);
 
   // A dQ-only call (the deterministic pair bwd_dq + bwd_dkv of the reference, whose dQ kernel sums in
-  // registers in key order) accumulates in ascending key-block order when the workspace holds the
+  // registers in key order) accumulates in a fixed key-block order when the workspace holds the
   // turn counters; otherwise, and in the combined call, the adds land in arrival order.
   const int64_t acc_bytes = bwd_accum_bytes(a), n_turn = bwd_turn_counters(a);
   const bool ordered = a->which == 1 && a->dq_accum_bytes >= acc_bytes + n_turn * 4;

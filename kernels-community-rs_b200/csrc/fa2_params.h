@@ -75,8 +75,8 @@ struct BwdParams {
   int head_dim;                         // real head dim (<= the kernel's D; columns beyond it are padding)
   // Ordered dQ accumulation (null = arrival order). dq_turn[((batch * heads + head) * num_mblk_q + query
   // block) * 4 + drain warp] counts the key blocks whose adds into those 32 rows have landed; it is
-  // zero at launch. A CTA adds only when the count equals the number of lower key blocks that add into the
-  // same rows, so every element is summed in ascending key-block order and dQ is bit-reproducible.
+  // zero at launch. A CTA adds only when the count equals the number of higher key blocks that add into the
+  // same rows, so every element is summed in descending key-block order and dQ is bit-reproducible.
   int* dq_turn;
   int num_mblk_q;                       // ceil(seqlen_q / 128)
 };

@@ -239,7 +239,7 @@ def test_forward_and_backward_other_head_dims(d, dtype):
 @pytest.mark.parametrize("causal", [True, False], ids=["causal", "full"])
 def test_dq_only_call_is_bit_reproducible(causal):
     """which = 1 (the deterministic bwd_dq of the reference, whose dQ kernel sums in registers in key
-    order, flash-attn2-rs/src/device/backward/dq.rs:278-279) adds the key blocks in ascending order:
+    order, flash-attn2-rs/src/device/backward/dq.rs:278-279) adds the key blocks in a fixed order:
     repeated runs give identical bits, also with many key blocks per query block and GQA."""
     from flash_attn2_b200 import cabi_ops as ops
     from oracle.attention_oracle import attention_backward
