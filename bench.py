@@ -320,7 +320,7 @@ def run_ours(args, rank, world):
                              "peak": peak, "unit": "TFLOP/s", "frac": tf(FWD_FLOPS, ms_fwd) / peak},
             "cpu_baseline": cpu,
             "e2e": None if ms_e2e is None else {"value": tf(total, ms_e2e), "unit": "TFLOP/s",
-                                                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                                                 "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
                                                  "ms_per_step": ms_e2e},
             "gpu_launches": 4 * args.steps,
             "clocks": clocks.summary(),
