@@ -29,24 +29,27 @@ __global__ void __launch_bounds__(256) preprocess_kernel(const PreprocessParams 
   const int64_t gid = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) / LANES;
   const int lane = threadIdx.x % LANES;
   const int64_t total = static_cast<int64_t>(p.batch) * p.seqlen_pad * p.heads;
-  if (gid >= total) return;
-  const int h = static_cast<int>(gid % p.heads);
-  const int64_t bs = gid / p.heads;
+  // No thread leaves before the shuffles below: a warp holds 32 / LANES groups, which may belong to
+  // different (batch, row) units when the head count is odd.
+  const bool in_range = gid < total;
+  const int h = static_cast<int>((in_range ? gid : 0) % p.heads);
+  const int64_t bs = (in_range ? gid : 0) / p.heads;
   const int s = static_cast<int>(bs % p.seqlen_pad);
   const int b = static_cast<int>(bs / p.seqlen_pad);
   int64_t row = s;     // row inside the input tensors
   int64_t drow = s;    // row inside delta
-  bool live = s < p.seqlen_q;
+  bool live = in_range && s < p.seqlen_q;
+  bool store = in_range;
   int bq = b;
   if (p.cu_q != nullptr) {
     const int q0 = p.cu_q[b];
     const int len = p.cu_q[b + 1] - q0;
-    live = s < len;
+    live = in_range && s < len;
     row = q0 + s;
     drow = q0 + 128 * b + s;
     bq = 0;
     // Padding of a packed sequence: only the 128-row tail that belongs to it.
-    if (s >= (len + 127) / 128 * 128) return;
+    if (s >= (len + 127) / 128 * 128) store = false;
   }
   float sum = 0.f;
   if (live) {
@@ -67,7 +70,7 @@ __global__ void __launch_bounds__(256) preprocess_kernel(const PreprocessParams 
   }
 #pragma unroll
   for (int d = LANES / 2; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d, LANES);
-  if (lane == 0) p.delta[bq * p.delta_batch_stride + h * p.delta_head_stride + drow] = sum;
+  if (lane == 0 && store) p.delta[bq * p.delta_batch_stride + h * p.delta_head_stride + drow] = sum;
 }
 
 template <bool BF16>

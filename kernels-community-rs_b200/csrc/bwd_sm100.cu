@@ -408,13 +408,13 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       if (it + 1 < n_iter) stat_next = load_stat(it + 1);
       if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 0);
       mbar_arrive(stat_full);
-      if (!mbar_wait(stat_full, it & 1, ctl, kWaitBwd + 15)) { ok = false; break; }
+      if (!warp_wait(stat_full, it & 1, ctl, kWaitBwd + 15)) { ok = false; break; }
       const float4* lse4 = reinterpret_cast<const float4*>(stat + wg * 64);
       const float4* dl4 = reinterpret_cast<const float4*>(stat + kBlk + wg * 64);
 
       // ---- phase A: P^T = exp2(S^T c - lse)
       if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 1);
-      if (!mbar_wait(s_full, it & 1, ctl, kWaitBwd + 11)) { ok = false; break; }
+      if (!warp_wait(s_full, it & 1, ctl, kWaitBwd + 11)) { ok = false; break; }
       if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 2);
       tc_fence_after();
       uint32_t sr[64];
@@ -490,7 +490,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 3);
 
       // ---- phase B: dS^T = P^T (dP^T - delta)
-      if (!mbar_wait(dp_full, it & 1, ctl, kWaitBwd + 12)) { ok = false; break; }
+      if (!warp_wait(dp_full, it & 1, ctl, kWaitBwd + 12)) { ok = false; break; }
       if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 4);
       tc_fence_after();
       tmem_ld32(t_dp, sr);
@@ -523,7 +523,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       const bool tma_store = (p.cu_k == nullptr) || (ti.n0 + kBlk <= ti.sk);
       uint8_t* stage = s_q + wg * Cfg::kTileBytes;
       bool done = true;
-      if (n_iter > 0) done = mbar_wait(dkv_done, 0, ctl, kWaitBwd + 13);
+      if (n_iter > 0) done = warp_wait(dkv_done, 0, ctl, kWaitBwd + 13);
       if (ct == 0) FA2_BSTAMP(905);
       if (done && store) {
         tc_fence_after();
@@ -580,7 +580,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         const int m0 = (ti.m_start + it % ti.n_m) * kBlk;
         const uint32_t st = it & 1;
         uint8_t* stage = s_do + st * Cfg::kTileBytes;
-        if (!mbar_wait(dq_full, it & 1, ctl, kWaitBwd + 14)) break;
+        if (!warp_wait(dq_full, it & 1, ctl, kWaitBwd + 14)) break;
         if (rt == 0 && it < 20) FA2_BSTAMP(640 + it * 4 + 0);
         tc_fence_after();
         uint32_t acc[D];

@@ -276,7 +276,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         const int tm_base = s * 256 + n_sfull * 8;
         if (tm_on) FA2_STAMP(tm_base + 0);
 #endif
-        if (!mbar_wait(&s_full[s], n_sfull & 1, ctl, kWaitSoftmaxSFull)) { ok = false; break; }
+        if (!warp_wait(&s_full[s], n_sfull & 1, ctl, kWaitSoftmaxSFull)) { ok = false; break; }
 #ifdef FA2_TIMING
         if (tm_on) FA2_STAMP(tm_base + 1);
 #endif
@@ -386,14 +386,14 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         if (j > nb_s) {
           // P V(j-1) has to be complete: it reads the P buffer that this iteration overwrites, and it is the
           // only operation that touches O of this stage.
-          if (!mbar_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitSoftmaxPvDone)) { ok = false; break; }
+          if (!warp_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitSoftmaxPvDone)) { ok = false; break; }
         } else {
           // First iteration of a tile: the TMA store of the previous tile must have read the buffer.
           if (row_in == 0) {
             tma_wait_group_read<0>();
             mbar_arrive(&o_stage_free[s]);
           }
-          if (!mbar_wait(&o_stage_free[s], n_first & 1, ctl, kWaitEpiFinal)) { ok = false; break; }
+          if (!warp_wait(&o_stage_free[s], n_first & 1, ctl, kWaitEpiFinal)) { ok = false; break; }
           ++n_first;
         }
         if (j > nb_s && __any_sync(0xffffffffu, grow)) {
@@ -407,6 +407,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             for (int i = 0; i < 16; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
             tmem_st16(t_o + c * 16, orr);
           }
+          // The rescaled O must be in TMEM before p_full lets the next P V accumulate onto it.
+          tmem_wait_st();
+          tc_fence_before();
         }
 #ifdef FA2_TIMING
         if (tm_on) FA2_STAMP(tm_base + 3);
@@ -497,7 +500,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
                        static_cast<int64_t>(ti.q_row0 + row) * p.o_row_stride + ti.h * p.o_head_stride;
       const bool tma_store = (p.cu_q == nullptr) || (r_lo + kBlockM <= ti.sq);
       if (ne_s > nb_s) {
-        if (!mbar_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitEpiPvDone)) break;
+        if (!warp_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitEpiPvDone)) break;
         tc_fence_after();
         uint32_t orr[D];
 #pragma unroll
@@ -527,14 +530,18 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         if (tma_store) {
           fence_proxy_async_smem();
           mbar_arrive(&epi_full[s]);
+          bool stored = true;
           if (row_in == 0) {
-            if (!mbar_wait(&epi_full[s], n_store & 1, ctl, kWaitEpiFinal)) break;
+            stored = mbar_wait(&epi_full[s], n_store & 1, ctl, kWaitEpiFinal);
+            if (stored) {
 #pragma unroll
-            for (int a = 0; a < Cfg::kAtoms; ++a)
-              if (a * 64 < p.head_dim)
-                tma_store_4d(&p.tm_o, stage_smem + a * (kBlockM * 128), a * 64, ti.h, ti.q_row0 + r_lo, ti.bq);
-            tma_commit_group();
+              for (int a = 0; a < Cfg::kAtoms; ++a)
+                if (a * 64 < p.head_dim)
+                  tma_store_4d(&p.tm_o, stage_smem + a * (kBlockM * 128), a * 64, ti.h, ti.q_row0 + r_lo, ti.bq);
+              tma_commit_group();
+            }
           }
+          if (!__all_sync(0xffffffffu, stored)) break;
           ++n_store;
         }
       } else {
@@ -554,6 +561,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         const float lse = (l > 0.f) ? (m + lg2(l)) * 0.6931471805599453f : INFINITY;
         p.lse_ptr[ti.bq * p.lse_batch_stride + ti.h * p.lse_head_stride + ti.q_row0 + row] = lse;
       }
+      __syncwarp();  // rows past the end of a packed sequence skipped the stores above
     }
     if (row_in == 0) tma_wait_group<0>();
   } else {

@@ -87,6 +87,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   return false;
 }
 
+// Wait of a whole warp. The vote brings the 32 lanes back together (they leave the polling loop in
+// different iterations) and makes the outcome warp-uniform, so that the .sync.aligned tcgen05
+// instructions that follow are executed by the converged warp.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, int code) {
+  const bool ok = mbar_wait(bar, parity, ctl, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // ---------------------------------------------------------------- fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
