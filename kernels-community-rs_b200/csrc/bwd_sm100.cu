@@ -408,13 +408,13 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       if (it + 1 < n_iter) stat_next = load_stat(it + 1);
       if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 0);
       mbar_arrive(stat_full);
-      if (!warp_wait(stat_full, it & 1, ctl, kWaitBwd + 15)) { ok = false; break; }
+      const bool stat_ok = mbar_wait(stat_full, it & 1, ctl, kWaitBwd + 15);  // voted on with s_full below
       const float4* lse4 = reinterpret_cast<const float4*>(stat + wg * 64);
       const float4* dl4 = reinterpret_cast<const float4*>(stat + kBlk + wg * 64);
 
       // ---- phase A: P^T = exp2(S^T c - lse)
       if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 1);
-      if (!warp_wait(s_full, it & 1, ctl, kWaitBwd + 11)) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(s_full, it & 1, ctl, kWaitBwd + 11) && stat_ok)) { ok = false; break; }
       if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 2);
       tc_fence_after();
       uint32_t sr[64];

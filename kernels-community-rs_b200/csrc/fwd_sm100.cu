@@ -383,20 +383,25 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             l *= alpha;
           }
         }
+        bool waited;
         if (j > nb_s) {
           // P V(j-1) has to be complete: it reads the P buffer that this iteration overwrites, and it is the
           // only operation that touches O of this stage.
-          if (!warp_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitSoftmaxPvDone)) { ok = false; break; }
+          waited = mbar_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitSoftmaxPvDone);
         } else {
           // First iteration of a tile: the TMA store of the previous tile must have read the buffer.
           if (row_in == 0) {
             tma_wait_group_read<0>();
             mbar_arrive(&o_stage_free[s]);
           }
-          if (!warp_wait(&o_stage_free[s], n_first & 1, ctl, kWaitEpiFinal)) { ok = false; break; }
+          waited = mbar_wait(&o_stage_free[s], n_first & 1, ctl, kWaitEpiFinal);
           ++n_first;
         }
-        if (j > nb_s && __any_sync(0xffffffffu, grow)) {
+        // One warp reduction reconverges the lanes after the wait and carries both warp-uniform
+        // decisions: bit 1 = a lane's wait ran out, bit 0 = a lane's row maximum grew.
+        const unsigned votes = __reduce_or_sync(0xffffffffu, (grow ? 1u : 0u) | (waited ? 0u : 2u));
+        if (votes & 2u) { ok = false; break; }
+        if (j > nb_s && (votes & 1u)) {
           tc_fence_after();
 #pragma unroll
           for (int c = 0; c < D / 16; ++c) {
@@ -530,18 +535,15 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         if (tma_store) {
           fence_proxy_async_smem();
           mbar_arrive(&epi_full[s]);
-          bool stored = true;
-          if (row_in == 0) {
-            stored = mbar_wait(&epi_full[s], n_store & 1, ctl, kWaitEpiFinal);
-            if (stored) {
+          // A wait that runs out here sets the abort flag; the warp then leaves together at its next
+          // warp_wait, which is also where the lanes meet again after this single-lane section.
+          if (row_in == 0 && mbar_wait(&epi_full[s], n_store & 1, ctl, kWaitEpiFinal)) {
 #pragma unroll
-              for (int a = 0; a < Cfg::kAtoms; ++a)
-                if (a * 64 < p.head_dim)
-                  tma_store_4d(&p.tm_o, stage_smem + a * (kBlockM * 128), a * 64, ti.h, ti.q_row0 + r_lo, ti.bq);
-              tma_commit_group();
-            }
+            for (int a = 0; a < Cfg::kAtoms; ++a)
+              if (a * 64 < p.head_dim)
+                tma_store_4d(&p.tm_o, stage_smem + a * (kBlockM * 128), a * 64, ti.h, ti.q_row0 + r_lo, ti.bq);
+            tma_commit_group();
           }
-          if (!__all_sync(0xffffffffu, stored)) break;
           ++n_store;
         }
       } else {
@@ -561,7 +563,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         const float lse = (l > 0.f) ? (m + lg2(l)) * 0.6931471805599453f : INFINITY;
         p.lse_ptr[ti.bq * p.lse_batch_stride + ti.h * p.lse_head_stride + ti.q_row0 + row] = lse;
       }
-      __syncwarp();  // rows past the end of a packed sequence skipped the stores above
+      // Rows past the end of a packed sequence skipped the stores above; the lanes meet again at the
+      // vote of the next warp_wait, before any aligned tcgen05 instruction.
     }
     if (row_in == 0) tma_wait_group<0>();
   } else {
