@@ -715,6 +715,13 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
     }
   }
   __syncwarp();
+  if (*abort_flag) {
+    // A wait ran out somewhere in this CTA. MMAs, commits and copies may still be in flight: give them
+    // about a millisecond to land before the barriers' memory and the TMEM columns are given back.
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) {
+    }
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == kMmaWarp) tmem_dealloc(tmem, 512);
