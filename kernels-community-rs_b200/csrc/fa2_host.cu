@@ -11,6 +11,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <atomic>
 #include <mutex>
@@ -123,6 +124,18 @@ int check_layout(const void* ptr, const int64_t* stride, int nstride, const char
     if (stride[i] % 8 != 0 || stride[i] < 0)
       return fail(FA2_E_VALUE, "%s: outer strides must be non-negative multiples of 8 elements", name);
   return FA2_OK;
+}
+
+// Debugging aid: with FA2_SYNC_LAUNCH=1 in the environment every launch of this library is followed by
+// a stream synchronise, so that an execution fault is reported by the call (and the kernel) that
+// raised it instead of by a later, unrelated one. Off by default: it serialises host and device.
+cudaError_t settle(cudaError_t launch_status, cudaStream_t stream) {
+  static const bool sync_launch = [] {
+    const char* v = std::getenv("FA2_SYNC_LAUNCH");
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+  }();
+  if (launch_status != cudaSuccess || !sync_launch) return launch_status;
+  return cudaStreamSynchronize(stream);
 }
 
 struct Windows {
@@ -274,7 +287,7 @@ int fwd_common(const fa2_fwd_args* a, void* stream_v, bool packed) {
   p.status = rt->status;
 
   p.head_dim = d;
-  cudaError_t e = fa2::launch_fwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream);
+  cudaError_t e = settle(fa2::launch_fwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream), stream);
   if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "forward launch failed: %s", cudaGetErrorString(e));
   return FA2_OK;
 }
@@ -321,7 +334,7 @@ int bwd_preprocess_impl(const fa2_bwd_preprocess_args* a, void* stream_v) {
   }
   if (packed)  // the 128-row gaps between packed sequences read as zero
     cudaMemsetAsync(a->delta, 0, static_cast<size_t>(p.delta_head_stride) * a->heads * 4, static_cast<cudaStream_t>(stream_v));
-  cudaError_t e = fa2::launch_bwd_preprocess(p, static_cast<cudaStream_t>(stream_v));
+  cudaError_t e = settle(fa2::launch_bwd_preprocess(p, static_cast<cudaStream_t>(stream_v)), static_cast<cudaStream_t>(stream_v));
   if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "preprocess launch failed: %s", cudaGetErrorString(e));
   return FA2_OK;
 }
@@ -470,7 +483,7 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
     return fail(FA2_E_RUNTIME, "memset failed: %s", cudaGetErrorString(e));
   if (a->ev_kernel_start != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_kernel_start), stream);
   p.head_dim = d;
-  e = fa2::launch_bwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream);
+  e = settle(fa2::launch_bwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream), stream);
   if (a->ev_kernel_stop != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_kernel_stop), stream);
   if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "backward launch failed: %s", cudaGetErrorString(e));
   if (want_dq && (e = fa2::launch_dq_convert(static_cast<const float*>(a->dq_accum), a->dq, n_dq, a->softmax_scale,
