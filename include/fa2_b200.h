@@ -164,10 +164,21 @@ FA2_API int fa2_pack_16bit(const void* src, void* dst, const int64_t shape[4], c
  *    that device current). Make that first call outside any stream capture;
  *  - all calls share the one accumulator: each call clears the part it uses, and two calls whose
  *    GPU work overlaps (different streams, or different threads) race on it. Serialise them;
- *  - the kernels' pipeline status of these calls lands in the library image too and is not what
- *    fa2_device_status() reads (that call allocates on first use). */
+ *  - the kernels' pipeline status of these calls lands in the library image too; read it with
+ *    fa2_bwd_static_status(), not fa2_device_status() (which reads the word of the allocating
+ *    entry points and allocates it on first use);
+ *  - lse and delta usually come from fa2_fwd and fa2_bwd_preprocess. fa2_bwd_preprocess allocates
+ *    nothing; fa2_fwd (like fa2_bwd and fa2_device_status) allocates one 64-byte status block per
+ *    device on its first call, so a host that cannot allocate later makes that first call while it
+ *    still can. */
 #define FA2_BWD_STATIC_MAX_ELEMENTS 4194304
 FA2_API int fa2_bwd_static(const fa2_bwd_args* args, void* stream);
+
+/* Status word of the fa2_bwd_static calls on `device`, with the meaning of fa2_device_status():
+ * synchronises the device, returns 0 when every pipeline wait of those calls completed, else the code
+ * of the first wait that ran out, and clears the word. It copies from and to the array in the
+ * library image and allocates nothing. No counterpart in the reference crate. */
+FA2_API int fa2_bwd_static_status(int device);
 
 /* Message of the last failed call on this thread ("" if none). */
 FA2_API const char* fa2_last_error(void);

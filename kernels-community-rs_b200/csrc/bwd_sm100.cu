@@ -99,7 +99,11 @@ __device__ __forceinline__ KvTile get_kv_tile(const BwdParams& p, int t) {
   // causal mask the first key blocks see the most query rows, so each head starts with its
   // heaviest CTAs.
   const int bh = t / p.num_nblk;
-  const int nblk = t - bh * p.num_nblk;
+  int nblk = t - bh * p.num_nblk;
+  // Ordered dQ accumulation waits for the higher key blocks of the same head. CTAs start in grid order, so
+  // there the highest key block comes first: a CTA only ever waits for CTAs that were started before it,
+  // whatever the number of key blocks and of resident CTAs.
+  if (p.dq_turn != nullptr) nblk = p.num_nblk - 1 - nblk;
   ti.b = bh / p.heads_k;
   ti.hk = bh - ti.b * p.heads_k;
   ti.n0 = nblk * kBlk;
@@ -603,8 +607,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           // Ordered mode: the key blocks that add into these rows take their turns in descending order,
           // which is the order in which they get there under a causal or sliding-window mask (a higher key
           // block starts at a later query block). This block's turn is the number of higher key blocks
-          // that cover the rows; a bounded wait for the slab's counter to reach it follows. The CTAs of
-          // one head are adjacent in the grid, so the blocks waited for are resident or next in line.
+          // that cover the rows; a bounded wait for the slab's counter to reach it follows. In this mode the
+          // grid lists a head's key blocks highest first (get_kv_tile), so the blocks waited for started earlier.
           const int mq = m0 / kBlk;
           int rank = 0;
           for (int nb = ti.n0 / kBlk + 1; nb < p.num_nblk; nb += 32) {

@@ -11,9 +11,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
-#include <cstdlib>
 #include <cstring>
-#include <atomic>
 #include <mutex>
 
 namespace {
@@ -41,17 +39,7 @@ struct Runtime {
   int* status = nullptr;  // device status word
 };
 constexpr int kMaxDevices = 64;
-constexpr int kStatusWords = 64;
-constexpr int kCounterBase = 16, kCounterSlots = 32;
-std::atomic<unsigned> g_launch_seq{0};
-
-// A zeroed device work counter for one backward launch. Launches take the slots in turn, so only
-// more than kCounterSlots launches in flight at once on one device could share one.
-int* next_counter(int* status_words, cudaStream_t stream) {
-  int* c = status_words + kCounterBase + (g_launch_seq.fetch_add(1) % kCounterSlots);
-  cudaMemsetAsync(c, 0, sizeof(int), stream);
-  return c;
-}
+constexpr int kStatusWords = 16;
 Runtime g_rt[kMaxDevices];
 std::mutex g_mu;
 EncodeTiledFn g_encode = nullptr;
@@ -77,7 +65,7 @@ int get_runtime(int device, Runtime** out) {
         return fail(FA2_E_RUNTIME, "cuTensorMapEncodeTiled is not available from the driver");
       g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
-    // word 0: kernel status; words 16..47: work counters handed to successive backward launches
+    // word 0: kernel status
     e = cudaMalloc(&rt.status, kStatusWords * sizeof(int));
     if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "cudaMalloc(status): %s", cudaGetErrorString(e));
     cudaMemset(rt.status, 0, kStatusWords * sizeof(int));
@@ -126,17 +114,33 @@ int check_layout(const void* ptr, const int64_t* stride, int nstride, const char
   return FA2_OK;
 }
 
-// Debugging aid: with FA2_SYNC_LAUNCH=1 in the environment every launch of this library is followed by
-// a stream synchronise, so that an execution fault is reported by the call (and the kernel) that
-// raised it instead of by a later, unrelated one. Off by default: it serialises host and device.
-cudaError_t settle(cudaError_t launch_status, cudaStream_t stream) {
-  static const bool sync_launch = [] {
-    const char* v = std::getenv("FA2_SYNC_LAUNCH");
-    return v != nullptr && v[0] != '\0' && v[0] != '0';
-  }();
-  if (launch_status != cudaSuccess || !sync_launch) return launch_status;
-  return cudaStreamSynchronize(stream);
-}
+// Makes the device that owns `ptr` current for the lifetime of the object and restores the caller's
+// device afterwards, as the reference binds the context of q before every launch
+// (flash-attn2-rs/src/host/forward/mod.rs:716-718). A pointer the runtime does not know (or a null
+// one) leaves the current device as it is.
+class DeviceScope {
+ public:
+  explicit DeviceScope(const void* ptr) {
+    cudaGetDevice(&prev_);
+    device_ = prev_;
+    cudaPointerAttributes attr;
+    if (ptr != nullptr && cudaPointerGetAttributes(&attr, ptr) == cudaSuccess &&
+        (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) && attr.device >= 0)
+      device_ = attr.device;
+    else
+      cudaGetLastError();  // an unknown pointer is not an error of this call
+    if (device_ != prev_) cudaSetDevice(device_);
+  }
+  ~DeviceScope() {
+    if (device_ != prev_) cudaSetDevice(prev_);
+  }
+  DeviceScope(const DeviceScope&) = delete;
+  DeviceScope& operator=(const DeviceScope&) = delete;
+  int device() const { return device_; }
+
+ private:
+  int prev_ = 0, device_ = 0;
+};
 
 struct Windows {
   int left, right, causal_alibi;
@@ -195,12 +199,10 @@ int fwd_common(const fa2_fwd_args* a, void* stream_v, bool packed) {
       return fail(FA2_E_VALUE, "cu_seqlens must be 4-byte aligned");
     if (a->total_q < 0 || a->total_k < 0) return fail(FA2_E_VALUE, "total_q and total_k must be non-negative");
   }
-  int device = 0;
-  cudaGetDevice(&device);
+  const DeviceScope scope(a->q);
   Runtime* rt = nullptr;
-  int rc = get_runtime(device, &rt);
+  int rc = get_runtime(scope.device(), &rt);
   if (rc != FA2_OK) return rc;
-  cudaSetDevice(device);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
   const int64_t rows_q = packed ? a->total_q : a->seqlen_q;
@@ -228,9 +230,15 @@ int fwd_common(const fa2_fwd_args* a, void* stream_v, bool packed) {
 
   if (packed && a->zero_tensors && a->seqlen_k != 0 && rows_k != 0) {
     // zero_tensors of the reference: out = 0, LSE = -inf before the kernel (varlen/mod.rs:419-444).
-    cudaMemsetAsync(a->out, 0, static_cast<size_t>(rows_q) * a->heads * d * 2, stream);
     const int64_t n = rows_q * a->heads;
-    fill_f32_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(a->lse, n, -INFINITY);
+    if (a->o_stride[2] == d && a->o_stride[1] == static_cast<int64_t>(a->heads) * d) {
+      cudaMemsetAsync(a->out, 0, static_cast<size_t>(n) * d * 2, stream);
+      fill_f32_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(a->lse, n, -INFINITY);
+    } else {  // a strided output view: clear only the elements that belong to it
+      fill_empty_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(
+          static_cast<uint16_t*>(a->out), a->lse, rows_q, a->heads, d, a->o_stride[1], a->o_stride[2], 0, rows_q,
+          a->total_q, 0, -INFINITY);
+    }
   }
   if (rows_k == 0 || a->seqlen_k == 0) {
     // No keys at all: O = 0, LSE = +inf (forward/mod.rs:548-582).
@@ -287,7 +295,7 @@ int fwd_common(const fa2_fwd_args* a, void* stream_v, bool packed) {
   p.status = rt->status;
 
   p.head_dim = d;
-  cudaError_t e = settle(fa2::launch_fwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream), stream);
+  cudaError_t e = fa2::launch_fwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream);
   if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "forward launch failed: %s", cudaGetErrorString(e));
   return FA2_OK;
 }
@@ -305,6 +313,7 @@ int bwd_preprocess_impl(const fa2_bwd_preprocess_args* a, void* stream_v) {
     return fail(FA2_E_VALUE, "dout, out and delta must be non-null");
   const int ns = packed ? 2 : 3;
   int rc;
+  const DeviceScope scope(a->dout);
   if ((rc = check_layout(a->dout, a->do_stride + (packed ? 1 : 0), ns, "dout")) != FA2_OK) return rc;
   if ((rc = check_layout(a->out, a->o_stride + (packed ? 1 : 0), ns, "out")) != FA2_OK) return rc;
   fa2::PreprocessParams p;
@@ -334,7 +343,7 @@ int bwd_preprocess_impl(const fa2_bwd_preprocess_args* a, void* stream_v) {
   }
   if (packed)  // the 128-row gaps between packed sequences read as zero
     cudaMemsetAsync(a->delta, 0, static_cast<size_t>(p.delta_head_stride) * a->heads * 4, static_cast<cudaStream_t>(stream_v));
-  cudaError_t e = settle(fa2::launch_bwd_preprocess(p, static_cast<cudaStream_t>(stream_v)), static_cast<cudaStream_t>(stream_v));
+  cudaError_t e = fa2::launch_bwd_preprocess(p, static_cast<cudaStream_t>(stream_v));
   if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "preprocess launch failed: %s", cudaGetErrorString(e));
   return FA2_OK;
 }
@@ -368,10 +377,9 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
     return fail(FA2_E_VALUE, "unsupported backward tensor dimensions");
   if ((a->which & 3) == 0) return fail(FA2_E_VALUE, "`which` selects no output");
   if (packed && a->cu_seqlens_k == nullptr) return fail(FA2_E_VALUE, "packed backward needs cu_seqlens_k");
-  int device = 0;
-  cudaGetDevice(&device);
+  const DeviceScope scope(a->q);
   Runtime* rt = nullptr;
-  int rc = get_runtime(device, &rt);
+  int rc = get_runtime(scope.device(), &rt);
   if (rc != FA2_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   const int64_t rows_q = packed ? a->total_q : a->seqlen_q;
@@ -470,7 +478,6 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
   p.scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.status = rt->status;
-  p.tile_counter = next_counter(rt->status, stream);
 
   // A dQ-only call (the deterministic pair bwd_dq + bwd_dkv of the reference, whose dQ kernel sums in
   // registers in key order) accumulates in a fixed key-block order when the workspace holds the
@@ -483,7 +490,7 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
     return fail(FA2_E_RUNTIME, "memset failed: %s", cudaGetErrorString(e));
   if (a->ev_kernel_start != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_kernel_start), stream);
   p.head_dim = d;
-  e = settle(fa2::launch_bwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream), stream);
+  e = fa2::launch_bwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream);
   if (a->ev_kernel_stop != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_kernel_stop), stream);
   if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "backward launch failed: %s", cudaGetErrorString(e));
   if (want_dq && (e = fa2::launch_dq_convert(static_cast<const float*>(a->dq_accum), a->dq, n_dq, a->softmax_scale,
@@ -581,10 +588,9 @@ int bwd_static_impl(const fa2_bwd_args* a, void* stream_v) {
   if (reinterpret_cast<uintptr_t>(a->dq) % 16 || reinterpret_cast<uintptr_t>(a->dk) % 16 ||
       reinterpret_cast<uintptr_t>(a->dv) % 16)
     return fail(FA2_E_VALUE, "dq, dk and dv must be 16-byte aligned");
-  int device = 0;
-  cudaGetDevice(&device);
+  const DeviceScope scope(a->q);
   StaticRuntime* rt = nullptr;
-  if ((rc = get_static_runtime(device, &rt)) != FA2_OK) return rc;
+  if ((rc = get_static_runtime(scope.device(), &rt)) != FA2_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
   fa2::BwdParams p;
@@ -637,7 +643,6 @@ int bwd_static_impl(const fa2_bwd_args* a, void* stream_v) {
   p.scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.status = rt->status;
-  p.tile_counter = next_counter(rt->status, stream);
 
   // The array keeps whatever the previous call left: the part this call adds into starts at zero.
   cudaError_t e = cudaMemsetAsync(rt->accum, 0, static_cast<size_t>(n_dq) * 4, stream);
@@ -676,6 +681,7 @@ int fa2_pack_16bit(const void* src, void* dst, const int64_t shape[4], const int
   if (src == nullptr || dst == nullptr) return fail(FA2_E_VALUE, "fa2_pack_16bit: null tensor");
   for (int i = 0; i < 4; ++i)
     if (shape[i] < 0 || shape[i] > INT32_MAX) return fail(FA2_E_VALUE, "fa2_pack_16bit: unsupported shape");
+  const DeviceScope scope(src);
   cudaError_t e = fa2::launch_pack_rows(src, dst, shape[0], shape[1], shape[2], shape[3], outer_strides[0],
                                         outer_strides[1], outer_strides[2], static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "packing copy launch failed: %s", cudaGetErrorString(e));
@@ -683,6 +689,30 @@ int fa2_pack_16bit(const void* src, void* dst, const int64_t shape[4], const int
 }
 
 int fa2_bwd_static(const fa2_bwd_args* args, void* stream) { return bwd_static_impl(args, stream); }
+
+int fa2_bwd_static_status(int device) {
+  int prev = 0;
+  cudaGetDevice(&prev);
+  if (device != prev && cudaSetDevice(device) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(FA2_E_VALUE, "device index %d cannot be selected", device);
+  }
+  StaticRuntime* rt = nullptr;
+  int rc = get_static_runtime(device, &rt);
+  int word = 0;
+  if (rc == FA2_OK) {
+    // Plain copies from and to the array inside the library image: nothing is allocated.
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(&word, rt->status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && word != 0) {
+      const int zero = 0;
+      e = cudaMemcpy(rt->status, &zero, sizeof(int), cudaMemcpyHostToDevice);
+    }
+    if (e != cudaSuccess) rc = fail(FA2_E_RUNTIME, "static status: %s", cudaGetErrorString(e));
+  }
+  if (device != prev) cudaSetDevice(prev);
+  return rc != FA2_OK ? rc : word;
+}
 
 
 int fa2_fwd(const fa2_fwd_args* args, void* stream) { return fwd_common(args, stream, false); }

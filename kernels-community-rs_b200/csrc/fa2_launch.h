@@ -8,8 +8,8 @@ namespace fa2 {
 // Dense and packed (varlen) forward; head_dim is a multiple of 8 up to 128 (kernels for D = 64 and 128).
 cudaError_t launch_fwd(const FwdParams& p, int head_dim, bool bf16, int num_sms, cudaStream_t stream);
 
-// dQ / dK / dV for head_dim a multiple of 8 up to 128; the fp32 dQ accumulator behind p.tm_dqa and the work counter
-// p.tile_counter must be zero.
+// dQ / dK / dV for head_dim a multiple of 8 up to 128; the fp32 dQ accumulator behind p.tm_dqa (and the turn
+// counters p.dq_turn, when given) must be zero.
 cudaError_t launch_bwd(const BwdParams& p, int head_dim, bool bf16, int num_sms, cudaStream_t stream);
 
 // delta = rowsum(dO * O) into the padded layouts (dense [B,H,Sq_pad], packed [H,total_q+128*B]).

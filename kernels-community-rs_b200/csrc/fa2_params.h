@@ -17,7 +17,6 @@ enum WaitSite : int {
   kWaitMmaSFree = 25,
   kWaitSoftmaxSFull = 31,
   kWaitSoftmaxPvDone = 32,
-  kWaitSoftmaxPair = 33,
   kWaitEpiFinal = 41,
   kWaitEpiPvDone = 42,
   kWaitBwd = 50,
@@ -66,7 +65,6 @@ struct BwdParams {
   int which;                            // bit 0: dQ, bit 1: dK and dV
   float scale, scale_log2;
   int* status;
-  int* tile_counter;                    // device work counter of this launch, zero at launch
   // Score transforms of the forward that the gradients have to follow (null / 0 when unused).
   const float* alibi;                   // [heads] or [batch, heads] slopes
   int alibi_batch_stride;

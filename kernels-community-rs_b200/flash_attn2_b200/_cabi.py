@@ -61,7 +61,7 @@ class BwdArgs(C.Structure):
 # Every symbol include/fa2_b200.h declares; the CPU test suite checks that the library exports them.
 EXPORTS = (
     "fa2_fwd", "fa2_varlen_fwd", "fa2_bwd_preprocess", "fa2_bwd_workspace_bytes", "fa2_bwd",
-    "fa2_bwd_static", "fa2_layout_is_addressable", "fa2_pack_16bit",
+    "fa2_bwd_static", "fa2_bwd_static_status", "fa2_layout_is_addressable", "fa2_pack_16bit",
     "fa2_last_error", "fa2_device_status", "fa2_sm_count",
 )
 
@@ -91,6 +91,8 @@ def load() -> C.CDLL:
         if hasattr(lib, "fa2_bwd_static"):
             lib.fa2_bwd_static.argtypes = [C.POINTER(BwdArgs), C.c_void_p]
             lib.fa2_bwd_static.restype = C.c_int
+            lib.fa2_bwd_static_status.argtypes = [C.c_int]
+            lib.fa2_bwd_static_status.restype = C.c_int
         lib.fa2_device_status.argtypes = [C.c_int]
         lib.fa2_device_status.restype = C.c_int
         lib.fa2_sm_count.argtypes = [C.c_int]

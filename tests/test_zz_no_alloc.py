@@ -3,7 +3,9 @@
 plugin host). It keeps the fp32 dQ accumulator in a device array inside the library image instead
 of taking one from the caller. The test calls it through the C ABI twice in a row - the shared
 array keeps the previous call's contents, so the second call proves it is cleared - and compares
-with fa2_bwd on the same inputs. It is collected last so that a failure here cannot hide others.
+with fa2_bwd and with the CPU oracle on the same inputs; the pipeline status of these calls is read
+with fa2_bwd_static_status, which allocates nothing either. It is collected last so that a failure
+here cannot hide others.
 """
 import ctypes as C
 
@@ -39,26 +41,30 @@ def _run_static(q, k, v, do, lse, delta, causal):
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     a = _args(q, k, v, do, lse, delta, dq, dk, dv, causal)  # dq_accum stays NULL: it is not used
     _cabi.check(lib.fa2_bwd_static(C.byref(a), torch.cuda.current_stream().cuda_stream))
-    torch.cuda.synchronize()
+    assert lib.fa2_bwd_static_status(torch.cuda.current_device()) == 0  # synchronises; 0 = no wait ran out
     return dq, dk, dv
 
 
 def test_static_backward_matches_fa2_bwd_twice_in_a_row():
     from flash_attn2_b200 import cabi_ops as ops
+    from oracle.attention_oracle import attention_backward
 
     tol = BWD_TOL[torch.bfloat16]
     # two different problems back to back: the second one reuses the accumulator the first one filled
     for seed, (b, h, hk, s), causal in ((11, (2, 4, 2, 384), True), (12, (1, 8, 8, 512), False)):
-        q, k, v, do = [t.cuda() for t in make_qkv(seed, b, h, hk, s, s, 128, torch.bfloat16, with_do=True)]
+        host = make_qkv(seed, b, h, hk, s, s, 128, torch.bfloat16, with_do=True)
+        q, k, v, do = [t.cuda() for t in host]
         out, lse = ops.fwd(q, k, v, causal=causal)
         delta = ops.bwd_preprocess(do, out)
         ref = ops.bwd(q, k, v, do, lse, delta, causal=causal)
         assert ops.device_status() == 0
+        oracle = attention_backward(*host, causal=causal, out=out.float().cpu(), lse=lse.cpu())[:3]
         for _ in range(2):
             got = _run_static(q, k, v, do, lse, delta, causal)
-            for g, r in zip(got, ref):
+            for g, r, o in zip(got, ref, oracle):
                 assert torch.isfinite(g.float()).all()
                 torch.testing.assert_close(g.float(), r.float(), atol=tol["atol"], rtol=tol["rtol"])
+                torch.testing.assert_close(g.float().cpu(), o, atol=tol["atol"], rtol=tol["rtol"])
             # dK and dV involve no atomics: bit-identical to the allocating entry point
             assert torch.equal(got[1], ref[1]) and torch.equal(got[2], ref[2])
 
