@@ -28,17 +28,6 @@
 
 namespace fa2 {
 
-#ifdef FA2_TIMING
-// Debug build only: clock64 stamps of CTA 0 (never compiled into the shipped library).
-__device__ long long g_bwd_timing[1024];
-#define FA2_BSTAMP(slot) \
-  do { if (blockIdx.x == 0 && (slot) < 1024) g_bwd_timing[(slot)] = clock64(); } while (0)
-extern "C" __attribute__((visibility("default"))) int fa2_debug_bwd_timing(long long* out, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(out, g_bwd_timing, sizeof(long long) * n));
-}
-#else
-#define FA2_BSTAMP(slot) do { } while (0)
-#endif
 
 namespace {
 
@@ -60,7 +49,7 @@ struct BwdCfg {
   static constexpr int kDSOff = 6 * kTileBytes;    // [128 keys x 128 q] 16-bit
   static constexpr int kDSBytes = kBlk * kBlk * 2;
   static constexpr int kBarOff = kDSOff + kDSBytes;
-  static constexpr int kNumBars = 24;
+  static constexpr int kNumBars = 26;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kStatOff = kMiscOff + 32;       // lse / delta: [2 buffers][2][128] fp32
   static constexpr int kSmemBytes = kStatOff + 2 * 2 * kBlk * 4;  // the dynamic window must start 1024-aligned
@@ -158,6 +147,9 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   uint64_t* stage_free = bars + 17;
   uint64_t* stage_full = bars + 18;
   uint64_t* epi_full = bars + 19;  // [2]
+  uint64_t* kv_fixed = bars + 21;  // packed batches: the fixer warp has cleared the rows past the sequence
+  uint64_t* q_fixed = bars + 22;   // [2]
+  uint64_t* do_fixed = bars + 24;  // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::kMiscOff + 8);
   float* s_stat = reinterpret_cast<float*>(smem + Cfg::kStatOff);
@@ -166,7 +158,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const WaitCtl ctl{abort_flag, p.status};
-  if (threadIdx.x == 0) FA2_BSTAMP(900);
   const KvTile ti = get_kv_tile(p, blockIdx.x);
   if (!ti.valid) return;
   const bool want_dq = (p.which & 1) != 0;
@@ -194,6 +185,11 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     mbar_init(stage_full, kBlk);
     mbar_init(&epi_full[0], kBlk);
     mbar_init(&epi_full[1], kBlk);
+    mbar_init(kv_fixed, 1);
+    for (int st = 0; st < 2; ++st) {
+      mbar_init(&q_fixed[st], 1);
+      mbar_init(&do_fixed[st], 1);
+    }
     mbar_fence_init();
     // The first loads go out before the rest of the CTA is set up (TMEM allocation, the block-wide
     // barrier): their latency is the longest item of a CTA's start.
@@ -231,7 +227,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const int n_iter = ti.n_iter;
-  if (threadIdx.x == 0) FA2_BSTAMP(901);
 
   if (warp < 4) {
     reg_dealloc<kMiscRegs>();
@@ -291,16 +286,34 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           mma_ss_o<o, o>(d_tmem, a, b, idesc_qk, ks.value > 0 ? 1u : 0u);
         });
       };
+      // Packed batches: a tile that reaches past the end of its sequence holds rows of the next sequence; it
+      // is usable once the fixer warp has cleared them. bit st of *_par: parity of the stage's next fix.
+      const bool packed = p.cu_q != nullptr;
+      uint32_t qfix_par = 0, dofix_par = 0;
+      auto ragged_q = [&](int it) { return packed && (ti.m_start + it % ti.n_m) * kBlk + kBlk > ti.sq; };
+      auto q_ready = [&](int it, uint32_t st, uint32_t ph, int code) -> bool {
+        if (!mbar_wait(&q_full[st], ph, ctl, code)) return false;
+        if (!ragged_q(it)) return true;
+        const uint32_t par = (qfix_par >> st) & 1;
+        qfix_par ^= 1u << st;
+        return mbar_wait(&q_fixed[st], par, ctl, kWaitBwd + 21);
+      };
+      auto do_ready = [&](int it, uint32_t st, uint32_t ph, int code) -> bool {
+        if (!mbar_wait(&do_full[st], ph, ctl, code)) return false;
+        if (!ragged_q(it)) return true;
+        const uint32_t par = (dofix_par >> st) & 1;
+        dofix_par ^= 1u << st;
+        return mbar_wait(&do_fixed[st], par, ctl, kWaitBwd + 22);
+      };
       bool ok = n_iter > 0;
       if (ok) ok = mbar_wait(kv_full, 0, ctl, kWaitBwd + 3);
-      FA2_BSTAMP(902);
-      if (ok) ok = mbar_wait(&q_full[0], 0, ctl, kWaitBwd + 4);
-      FA2_BSTAMP(903);
+      if (ok && packed && ti.n0 + kBlk > ti.sk) ok = mbar_wait(kv_fixed, 0, ctl, kWaitBwd + 20);
+      if (ok) ok = q_ready(0, 0, 0, kWaitBwd + 4);
       if (ok) {
         tc_fence_after();
         kmajor_pair(tmem + Cfg::kTmemS, k_kmaj, q_kmaj);
         mma_commit(s_full);
-        ok = mbar_wait(&do_full[0], 0, ctl, kWaitBwd + 5);
+        ok = do_ready(0, 0, 0, kWaitBwd + 5);
       }
       if (ok) {
         tc_fence_after();
@@ -313,10 +326,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         const bool has_next = it + 1 < n_iter;
         const uint32_t acc = it > 0 ? 1u : 0u;
         // dV += P^T dO   (P^T: two 32-column halves at S + 0 and S + 64)
-        if (it < 20) FA2_BSTAMP(256 + it * 16 + 0);
         ok = mbar_wait(p_full, it & 1, ctl, kWaitBwd + 6);
         if (!ok) break;
-        if (it < 20) FA2_BSTAMP(256 + it * 16 + 1);
         tc_fence_after();
         {
           const uint64_t b = do_mn + st * kTile16;
@@ -326,11 +337,9 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           });
         }
         mma_commit(&do_empty[st]);
-        if (it < 20) FA2_BSTAMP(256 + it * 16 + 2);
         // dQ = dS K   (into the dP^T columns, which the compute warps have drained)
         ok = mbar_wait(ds_full, it & 1, ctl, kWaitBwd + 7);
         if (!ok) break;
-        if (it < 20) FA2_BSTAMP(256 + it * 16 + 3);
         tc_fence_after();
         if (want_dq) {
           static_for<kBlk / 16>([&](auto ks) {
@@ -339,16 +348,14 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           });
           mma_commit(dq_full);
         }
-        if (it < 20) FA2_BSTAMP(256 + it * 16 + 4);
         // S^T of the next iteration
         if (has_next) {
-          ok = mbar_wait(&q_full[st ^ 1], nph, ctl, kWaitBwd + 8);
+          ok = q_ready(it + 1, st ^ 1, nph, kWaitBwd + 8);
           if (!ok) break;
           tc_fence_after();
           kmajor_pair(tmem + Cfg::kTmemS, k_kmaj, q_kmaj + (st ^ 1) * kTile16);
           mma_commit(s_full);
         }
-        if (it < 20) FA2_BSTAMP(256 + it * 16 + 5);
         // dK += dS^T Q
         {
           const uint64_t b = q_mn + st * kTile16;
@@ -358,22 +365,61 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           });
         }
         mma_commit(&q_empty[st]);
-        if (it < 20) FA2_BSTAMP(256 + it * 16 + 6);
         // dP^T of the next iteration, once the dQ tile has left TMEM
         if (has_next) {
-          ok = mbar_wait(&do_full[st ^ 1], nph, ctl, kWaitBwd + 9);
-          if (it < 20) FA2_BSTAMP(256 + it * 16 + 7);
+          ok = do_ready(it + 1, st ^ 1, nph, kWaitBwd + 9);
           if (ok && want_dq) ok = mbar_wait(dq_free, it & 1, ctl, kWaitBwd + 10);
           if (!ok) break;
-          if (it < 20) FA2_BSTAMP(256 + it * 16 + 8);
           tc_fence_after();
           kmajor_pair(tmem + Cfg::kTmemDP, v_kmaj, do_kmaj + (st ^ 1) * kTile16);
           mma_commit(dp_full);
-          if (it < 20) FA2_BSTAMP(256 + it * 16 + 9);
         }
       }
       if (ok) mma_commit(dkv_done);
-      FA2_BSTAMP(904);
+    } else if (warp == 2 && p.cu_q != nullptr && n_iter > 0) {
+      // ---------------------------------------------------------------- fixer (packed batches)
+      // The reference zero-fills the rows of a tile that lie past the end of the sequence while staging it
+      // (flash-attn2-rs/src/device/varlen/backward.rs:134-648 through the zfill copies of
+      // src/device/forward/mod.rs:171-175); the TMA boxes here carry the next sequence's rows instead, and
+      // a zero probability times a NaN or Inf of a neighbour would still poison dK, dV and dQ. This warp
+      // waits for every Q and dO tile (which keeps it in step with the loader) and clears the stray rows
+      // of those that need it, and of K and V once.
+      auto clear_rows = [&](uint8_t* tile, int first) {
+        for (int r = first + (lane >> 3); r < kBlk; r += 4)
+#pragma unroll
+          for (int a = 0; a < Cfg::kAtoms; ++a)
+            *reinterpret_cast<uint4*>(tile + a * (kBlk * 128) + r * 128 + (lane & 7) * 16) = make_uint4(0, 0, 0, 0);
+      };
+      auto publish = [&](uint64_t* bar) {
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar);
+        __syncwarp();
+      };
+      bool ok = true;
+      const int kv_first = ti.sk - ti.n0;
+      if (kv_first < kBlk) {
+        ok = __all_sync(0xffffffffu, mbar_wait(kv_full, 0, ctl, kWaitBwd + 3));
+        if (ok) {
+          clear_rows(s_k, kv_first);
+          clear_rows(s_v, kv_first);
+          publish(kv_fixed);
+        }
+      }
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int first = ti.sq - (ti.m_start + it % ti.n_m) * kBlk;
+        const uint32_t st = it & 1, ph = (it >> 1) & 1;
+        ok = __all_sync(0xffffffffu, mbar_wait(&q_full[st], ph, ctl, kWaitBwd + 4));
+        if (ok && first < kBlk) {
+          clear_rows(s_q + st * Cfg::kTileBytes, first);
+          publish(&q_fixed[st]);
+        }
+        ok = ok && __all_sync(0xffffffffu, mbar_wait(&do_full[st], ph, ctl, kWaitBwd + 5));
+        if (ok && first < kBlk) {
+          clear_rows(s_do + st * Cfg::kTileBytes, first);
+          publish(&do_fixed[st]);
+        }
+      }
     }
   } else if (warp < 12) {
     // ------------------------------------------------------------------ compute
@@ -410,16 +456,13 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       float* stat = s_stat + (it & 1) * (2 * kBlk);
       stat[ct] = stat_next;
       if (it + 1 < n_iter) stat_next = load_stat(it + 1);
-      if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 0);
       mbar_arrive(stat_full);
       const bool stat_ok = mbar_wait(stat_full, it & 1, ctl, kWaitBwd + 15);  // voted on with s_full below
       const float4* lse4 = reinterpret_cast<const float4*>(stat + wg * 64);
       const float4* dl4 = reinterpret_cast<const float4*>(stat + kBlk + wg * 64);
 
       // ---- phase A: P^T = exp2(S^T c - lse)
-      if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 1);
       if (!__all_sync(0xffffffffu, mbar_wait(s_full, it & 1, ctl, kWaitBwd + 11) && stat_ok)) { ok = false; break; }
-      if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 2);
       tc_fence_after();
       uint32_t sr[64];
       tmem_ld32(t_s, sr);
@@ -491,11 +534,9 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(p_full);
-      if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 3);
 
       // ---- phase B: dS^T = P^T (dP^T - delta)
       if (!warp_wait(dp_full, it & 1, ctl, kWaitBwd + 12)) { ok = false; break; }
-      if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 4);
       tc_fence_after();
       tmem_ld32(t_dp, sr);
       tmem_ld32(t_dp + 32, sr + 32);
@@ -515,7 +556,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       }
       fence_proxy_async_smem();
       mbar_arrive(ds_full);
-      if (ct == 0 && it < 20) FA2_BSTAMP(it * 8 + 5);
     }
     // ---- epilogue: warpgroup 0 writes dK (scaled), warpgroup 1 writes dV
     if (ok) {
@@ -528,7 +568,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       uint8_t* stage = s_q + wg * Cfg::kTileBytes;
       bool done = true;
       if (n_iter > 0) done = warp_wait(dkv_done, 0, ctl, kWaitBwd + 13);
-      if (ct == 0) FA2_BSTAMP(905);
       if (done && store) {
         tc_fence_after();
         uint16_t* grow = gptr + ti.bq * p.dkv_batch_stride + static_cast<int64_t>(ti.k_row0 + kpos) * p.dkv_row_stride +
@@ -563,7 +602,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
             for (int a = 0; a < Cfg::kAtoms; ++a)
               if (a * 64 < p.head_dim) tma_store_4d(tm, stage + a * (kBlk * 128), a * 64, ti.hk, ti.k_row0 + ti.n0, ti.bq);
             tma_commit_group();
-            tma_wait_group<0>();
+            tma_wait_group_read<0>();  // the staging tile must outlive the copy's reads, not its writes
           }
         }
       }
@@ -574,7 +613,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     // for the next iteration right away; it then leaves through the dO stage this iteration has
     // retired as cp.reduce.async.bulk adds into the accumulator.
     reg_alloc<kDrainRegs>();
-    const int rt = tid - 384;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_dq = tmem + lane_addr + Cfg::kTmemDP;
     if (want_dq) {
@@ -585,7 +623,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         const uint32_t st = it & 1;
         uint8_t* stage = s_do + st * Cfg::kTileBytes;
         if (!warp_wait(dq_full, it & 1, ctl, kWaitBwd + 14)) break;
-        if (rt == 0 && it < 20) FA2_BSTAMP(640 + it * 4 + 0);
         tc_fence_after();
         uint32_t acc[D];
 #pragma unroll
@@ -593,7 +630,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(dq_free);
-        if (rt == 0 && it < 20) FA2_BSTAMP(640 + it * 4 + 1);
         // Each warp drains its own 32 rows: pieces of 32 fp32 columns (4 KB) roll through the warp's share
         // of the stage (two buffers at D = 128). Piece k is staged as soon as the reduce of piece k - kBufs
         // has read its buffer, so the reduce engine always has a piece queued, and nothing but the warp
@@ -664,7 +700,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         if (lane == 0) {
           tma_wait_group_read<0>();
           mbar_arrive(&do_empty[st]);
-          if (rt == 0 && it < 20) FA2_BSTAMP(640 + it * 4 + 2);
           if (turn != nullptr) {
             // The adds have to be in memory before the next key block may start on these rows.
             tma_wait_group<0>();
@@ -674,7 +709,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           }
         }
       }
-      if (lane == 0) tma_wait_group<0>();
+      if (lane == 0) tma_wait_group_read<0>();
     }
   }
   __syncwarp();
@@ -687,7 +722,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) FA2_BSTAMP(906);
   if (warp == 1) tmem_dealloc(tmem, 512);
 }
 

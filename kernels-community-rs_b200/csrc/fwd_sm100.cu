@@ -2,23 +2,35 @@
 //
 // One persistent CTA per SM walks a longest-first list of work tiles. A work tile is 256 query
 // rows of one (batch, head): two 128-row "stages" that run independently of each other and share
-// the K/V tiles in shared memory.
+// the K/V tiles in shared memory. 512 threads in four warpgroups:
 //
 //   warps 0-3    stage 0 } softmax: tcgen05.ld one S row per thread (the S region of TMEM is handed back
 //   warps 4-7    stage 1 }   to the MMA warp at once, so the next Q K^T runs under this softmax) -> mask,
 //                            row max, exp2, row sum -> bf16/fp16 P written to shared memory in pieces, as the
 //                            K-major swizzled A operand of P V; O in TMEM is rescaled only when the row max
-//                            grew by more than 2^8. At the end of a tile the same warps run the stage's
-//                            epilogue: O / l -> 16-bit -> swizzled smem (the P buffer) -> TMA store
-//                            (predicated stores on ragged packed tiles), LSE = (m + log2 l) ln 2.
-//   warp 8, 10   mma      : one thread per stage issues tcgen05.mma; S = Q K^T (smem x smem) into TMEM one
+//                            grew by more than 2^8. At the end of a tile the warps leave the row's (max, sum)
+//                            in shared memory and go straight on to the next tile.
+//   warps 8-11   epilogue : when the last P V of a stage's tile has completed: O from TMEM, O / l -> 16-bit
+//                           -> global memory (one row per thread, predicated on the row and the head dim),
+//                           LSE = (m + log2 l) ln 2; rows that see no key get O = 0 and LSE = +inf. The O
+//                           columns are handed back as soon as they are in registers.
+//   warp 12, 13  mma      : one thread per stage issues tcgen05.mma; S = Q K^T (smem x smem) into TMEM one
 //                           key tile ahead, O += P V (smem x smem, V as an MN-major operand) piece by piece
-//   warp 9       loader   : TMA (cp.async.bulk.tensor, 128B swizzle) Q stages + K/V ring in the order
-//                           K(0) K(1) V(0) K(2) V(1) ...
+//   warp 14      loader   : TMA (cp.async.bulk.tensor, 128B swizzle) Q stages + K/V ring in the order
+//                           K(0) K(1) V(0) K(2) V(1) ...; it leaves last, after every commit on its
+//                           barriers has landed
+//   warp 15      fixer    : packed batches only. The rows of a V tile that lie past the end of the sequence
+//                           belong to the next sequence (P is exactly zero there, but 0 x NaN is NaN); it
+//                           clears them in shared memory once the tile has landed, before the MMA threads
+//                           may read it (the reference zero-fills them while staging,
+//                           flash-attn2-rs/src/device/forward/mod.rs:171-175,200). Stray K rows only reach
+//                           score columns that the mask replaces.
 //
 // A stage never waits for the other one: each has its own issuing thread, barriers and counters, and a
 // K/V ring slot is released by one commit of each issuer, so stage 0 may already work on the next tile
-// while stage 1 finishes the current one.
+// while stage 1 finishes the current one. Every asynchronous arrival (TMA bytes, tcgen05.commit) has a
+// waiter before the CTA ends, and no thread of a warp that executes .sync.aligned tcgen05 instructions runs
+// lane-divergent code other than bounded polling loops that end in a warp vote.
 //
 // Replaces the reference kernels flash_attn_fwd / varlen_fwd
 // (flash-attn2-rs/src/device/forward/dense.rs:472-590, forward/mod.rs:1162-1407,
@@ -31,37 +43,23 @@
 #ifndef FA2_PQ
 #define FA2_PQ 4
 #endif
-#ifndef FA2_POLY_PAIRS
-#define FA2_POLY_PAIRS 0
-#endif
 
 namespace fa2 {
-
-#ifdef FA2_TIMING
-// Debug build only: clock64 stamps of CTA 0 (never compiled into the shipped library).
-__device__ long long g_fwd_timing[1024];
-#define FA2_STAMP(slot) \
-  do { if (blockIdx.x == 0 && (slot) < 1024) g_fwd_timing[(slot)] = clock64(); } while (0)
-extern "C" __attribute__((visibility("default"))) int fa2_debug_fwd_timing(long long* out, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(out, g_fwd_timing, sizeof(long long) * n));
-}
-#else
-#define FA2_STAMP(slot) do { } while (0)
-#endif
 
 namespace {
 
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
-constexpr int kThreads = 384;   // 8 softmax warps + one warpgroup holding the MMA and the loader warp
-constexpr int kMmaWarp = 8;   // issues the MMAs of stage 0
-constexpr int kMmaWarp1 = 10;  // issues the MMAs of stage 1
-constexpr int kLoadWarp = 9;
-constexpr int kSoftmaxRegs = 200;
-constexpr int kOtherRegs = 104;
-constexpr int kPQ = FA2_PQ;                        // P is handed to the MMA warp in kPQ pieces of kBlockN / kPQ keys
+constexpr int kThreads = 512;
+constexpr int kEpiWarp = 8;    // first warp of the epilogue warpgroup
+constexpr int kMmaWarp = 12;   // issues the MMAs of stage 0 (warp 13: stage 1); owns the TMEM allocation
+constexpr int kLoadWarp = 14;
+constexpr int kFixWarp = 15;
+constexpr int kSoftmaxRegs = 184;
+constexpr int kEpiRegs = 64;
+constexpr int kOtherRegs = 80;
+constexpr int kPQ = FA2_PQ;                // P is handed to the MMA warp in kPQ pieces of kBlockN / kPQ keys
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain
-constexpr int kPolyPairs = FA2_POLY_PAIRS;    // of every 4 score pairs, how many take exp2 on the FMA pipe
 
 template <int D>
 struct FwdCfg {
@@ -70,15 +68,14 @@ struct FwdCfg {
   static constexpr int kSlots = (D == 128) ? 3 : 6;        // K/V ring depth
   static constexpr int kQOff = 0;
   static constexpr int kKVOff = 2 * kTileBytes;
-  // One buffer per stage that holds P (128 x 128 16-bit, the A operand of P V) during the key loop and
-  // the output tile for the TMA store in the epilogue.
+  // One buffer per stage that holds P (128 x 128 16-bit, the A operand of P V).
   static constexpr int kPBytes = kBlockM * kBlockN * 2;
-  static constexpr int kStageBufBytes = kTileBytes > kPBytes ? kTileBytes : kPBytes;
-  static constexpr int kOOff = kKVOff + kSlots * kTileBytes;
-  static constexpr int kBarOff = kOOff + 2 * kStageBufBytes;
-  static constexpr int kNumBars = 2 * kSlots + 18 + 2 * kPQ;
+  static constexpr int kPOff = kKVOff + kSlots * kTileBytes;
+  static constexpr int kBarOff = kPOff + 2 * kPBytes;
+  static constexpr int kNumBars = 3 * kSlots + 2 * (9 + kPQ);  // kv_full, kv_empty, kv_fixed + per stage
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;  // tmem slot, abort flag
-  static constexpr int kSmemBytes = kMiscOff + 32;  // the dynamic window must start 1024-aligned
+  static constexpr int kStatOff = kMiscOff + 32;           // [2 stages][128 rows] (max, sum) fp32
+  static constexpr int kSmemBytes = kStatOff + 2 * kBlockM * 8;  // the dynamic window must start 1024-aligned
   static constexpr uint32_t kTmemS0 = 0, kTmemS1 = 128, kTmemO0 = 256, kTmemO1 = 256 + D;
 };
 
@@ -118,8 +115,9 @@ __device__ __forceinline__ Tile get_tile(const FwdParams& p, int t) {
     ti.k_row0 = p.cu_k[ti.b];
     ti.sk = p.cu_k[ti.b + 1] - ti.k_row0;
     ti.bq = 0;
-    // Inconsistent metadata is skipped, as the reference kernel does.
-    if (ti.sq < 0 || ti.sk < 0 || ti.sq > p.seqlen_q || ti.sk > p.seqlen_k) ti.sq = 0;
+    // Inconsistent metadata is skipped, as the reference kernel does
+    // (flash-attn2-rs/src/device/varlen/mod.rs:112-127).
+    if (ti.sq < 0 || ti.sk < 0 || ti.sq > p.seqlen_q || ti.sk > p.seqlen_k || ti.q_row0 < 0 || ti.k_row0 < 0) ti.sq = 0;
   } else {
     ti.q_row0 = 0;
     ti.k_row0 = 0;
@@ -157,6 +155,14 @@ __device__ __forceinline__ Tile get_tile(const FwdParams& p, int t) {
   return ti;
 }
 
+// First row of key tile j that lies past the end of a packed sequence (kBlockN = none). Dense tensors need
+// nothing: the TMA unit fills rows past the tensor with zeros.
+__device__ __forceinline__ int ragged_row(const FwdParams& p, const Tile& ti, int j) {
+  if (p.cu_q == nullptr) return kBlockN;
+  const int left = ti.sk - j * kBlockN;
+  return left < kBlockN ? max(left, 0) : kBlockN;
+}
+
 __device__ __forceinline__ float tanh_approx(float x) {
   float y;
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -174,51 +180,50 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   }
   uint8_t* s_q = smem + Cfg::kQOff;
   uint8_t* s_kv = smem + Cfg::kKVOff;
-  uint8_t* s_o = smem + Cfg::kOOff;
+  uint8_t* s_p = smem + Cfg::kPOff;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOff);
-  uint64_t* kv_full = bars;
-  uint64_t* kv_empty = bars + Cfg::kSlots;
-  uint64_t* q_full = bars + 2 * Cfg::kSlots;  // every array below is [2], one per stage
-  uint64_t* q_empty = q_full + 2;
-  uint64_t* s_full = q_full + 4;
-  uint64_t* s_free = q_full + 16;        // S_s has been read out of TMEM: the next Q K^T may overwrite it
-  uint64_t* p_full = q_full + 18;        // [2][kPQ]: piece q of P_s is in shared memory
-  uint64_t* pv_done = q_full + 8;
-  uint64_t* o_free = q_full + 10;        // O_s has been read out of TMEM
-  uint64_t* epi_full = q_full + 12;      // all 128 rows of O_s are staged in smem
-  uint64_t* o_stage_free = q_full + 14;  // the previous TMA store of stage s has read its staging tile
+  uint64_t* kv_full = bars;                    // TMA bytes of the slot's tile have landed
+  uint64_t* kv_empty = bars + Cfg::kSlots;     // both issuers' MMAs on the slot have completed
+  uint64_t* kv_fixed = bars + 2 * Cfg::kSlots; // the fixer has cleared the stray rows of a ragged V tile
+  uint64_t* st_bars = bars + 3 * Cfg::kSlots;  // every array below is [2], one per stage
+  uint64_t* q_full = st_bars;
+  uint64_t* q_empty = st_bars + 2;
+  uint64_t* s_full = st_bars + 4;
+  uint64_t* s_free = st_bars + 6;       // S_s has been read out of TMEM: the next Q K^T may overwrite it
+  uint64_t* pv_done = st_bars + 8;      // P V(j) of stage s has completed: P_s may be overwritten, O_s rescaled
+  uint64_t* o_full = st_bars + 10;      // the last P V of the stage's tile has completed
+  uint64_t* o_free = st_bars + 12;      // O_s has been read out of TMEM by the epilogue
+  uint64_t* stat_full = st_bars + 14;   // the softmax warps have left (max, sum) of the tile's rows
+  uint64_t* stat_free = st_bars + 16;   // the epilogue has read them
+  uint64_t* p_full = st_bars + 18;      // [2][kPQ]: piece q of P_s is in shared memory
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::kMiscOff + 8);
+  float2* s_stat = reinterpret_cast<float2*>(smem + Cfg::kStatOff);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const WaitCtl ctl{abort_flag, p.status};
-#ifdef FA2_TIMING
-  if (tid == 0 && blockIdx.x == 0) {
-    unsigned long long gt;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
-    g_fwd_timing[1000] = clock64();
-    g_fwd_timing[1001] = static_cast<long long>(gt);
-  }
-#endif
+  const bool packed = p.cu_q != nullptr;
 
   if (tid == 0) {
     *abort_flag = 0;
     for (int i = 0; i < Cfg::kSlots; ++i) {
       mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 2);  // one commit per stage cursor of the MMA warp
+      mbar_init(&kv_empty[i], 2);  // one commit per issuer
+      mbar_init(&kv_fixed[i], 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&q_full[s], 1);
       mbar_init(&q_empty[s], 1);
       mbar_init(&s_full[s], 1);
-      for (int q = 0; q < kPQ; ++q) mbar_init(&p_full[s * kPQ + q], kBlockM);
-      mbar_init(&pv_done[s], 1);
-      mbar_init(&o_free[s], kBlockM);
       mbar_init(&s_free[s], kBlockM);
-      mbar_init(&epi_full[s], kBlockM);
-      mbar_init(&o_stage_free[s], 1);
+      mbar_init(&pv_done[s], 1);
+      mbar_init(&o_full[s], 1);
+      mbar_init(&o_free[s], kBlockM);
+      mbar_init(&stat_full[s], kBlockM);
+      mbar_init(&stat_free[s], kBlockM);
+      for (int q = 0; q < kPQ; ++q) mbar_init(&p_full[s * kPQ + q], kBlockM);
     }
     mbar_fence_init();
   }
@@ -230,7 +235,6 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
     tma_prefetch_desc(&p.tm_q);
     tma_prefetch_desc(&p.tm_k);
     tma_prefetch_desc(&p.tm_v);
-    tma_prefetch_desc(&p.tm_o);
   }
   tc_fence_before();
   __syncthreads();
@@ -238,48 +242,37 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   const uint32_t tmem = *tmem_slot;
 
   if (warp < 8) {
-    // ------------------------------------------------------------------ softmax + epilogue of stage s
+    // ------------------------------------------------------------------ softmax of stage s
     reg_alloc<kSoftmaxRegs>();
     const int s = warp >> 2;
     const int row_in = tid & 127;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_s = tmem + lane_addr + (s == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1);
     const uint32_t t_o = tmem + lane_addr + (s == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
-    uint8_t* stage_smem = s_o + s * Cfg::kStageBufBytes;
     // P of this stage as the K-major, 128-byte swizzled A operand of P V: key chunk c (8 keys, 16 bytes) of
     // row r sits in atom c / 8 at byte 128 r + 16 ((c % 8) ^ (r % 8)).
-    const uint32_t p_row = smem_u32(stage_smem) + row_in * 128;
+    const uint32_t p_row = smem_u32(s_p + s * Cfg::kPBytes) + row_in * 128;
     const uint32_t p_swz = static_cast<uint32_t>(row_in & 7) << 4;
     auto store_p_chunk = [&](const int c, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
       const uint32_t addr = p_row + (c >> 3) * (kBlockM * 128) + ((static_cast<uint32_t>(c & 7) << 4) ^ p_swz);
       asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
     };
     const bool fancy = (p.softcap > 0.f) || (p.alibi != nullptr) || (p.scale_log2 < 0.f);
-    uint32_t n_sfull = 0, n_pv = 0, n_store = 0, n_first = 0;
-#ifdef FA2_TIMING
-    int tm_tile = 0;
-#endif
-    for (int t = blockIdx.x; t - static_cast<int>(blockIdx.x) < p.num_tiles; t += gridDim.x) {
+    uint32_t n_sfull = 0, n_pv = 0, n_tile = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t - static_cast<int>(blockIdx.x) < p.num_tiles && ok; t += gridDim.x) {
       const Tile ti = get_tile(p, t);
       if (!ti.valid) continue;
-      const int r_lo = ti.m0 + s * kBlockM;
-      const int row = r_lo + row_in;
       const int nb_s = s ? ti.nb[1] : ti.nb[0];
       const int ne_s = s ? ti.ne[1] : ti.ne[0];
+      if (ne_s <= nb_s) continue;  // no key is visible to this stage: the epilogue writes O = 0, LSE = +inf
+      const int r_lo = ti.m0 + s * kBlockM;
+      const int row = r_lo + row_in;
       float m = -INFINITY, l = 0.f;
       float slope = 0.f;
       if (p.alibi != nullptr) slope = p.alibi[ti.b * p.alibi_batch_stride + ti.h] * 1.4426950408889634f;
-      bool ok = true;
       for (int j = nb_s; j < ne_s; ++j) {
-#ifdef FA2_TIMING
-        const bool tm_on = (row_in == 0) && n_sfull < 28;
-        const int tm_base = s * 256 + n_sfull * 8;
-        if (tm_on) FA2_STAMP(tm_base + 0);
-#endif
         if (!warp_wait(&s_full[s], n_sfull & 1, ctl, kWaitSoftmaxSFull)) { ok = false; break; }
-#ifdef FA2_TIMING
-        if (tm_on) FA2_STAMP(tm_base + 1);
-#endif
         ++n_sfull;
         tc_fence_after();
         uint32_t sr[kBlockN];
@@ -288,9 +281,6 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(&s_free[s]);  // the scores live in registers from here on
-#ifdef FA2_TIMING
-        if (tm_on) FA2_STAMP(tm_base + 2);
-#endif
         float cs = p.scale_log2;
         const int col0 = j * kBlockN;
         // Tiles that touch no mask boundary (warp-uniform test on the stage's row range) and need
@@ -336,23 +326,21 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             l *= alpha;
           }
         } else {
-          if (fancy) {
-            // Scores leave this block already in the log2 domain.
-            const float inv_cap = (p.softcap > 0.f) ? p.scale / p.softcap : 0.f;
-            const float cap_l2 = p.softcap * 1.4426950408889634f;
-  #pragma unroll
-            for (int i = 0; i < kBlockN; ++i) {
-              float x = __uint_as_float(sr[i]);
-              x = (p.softcap > 0.f) ? cap_l2 * tanh_approx(x * inv_cap) : x * p.scale_log2;
-              if (p.alibi != nullptr) {
-                const int col = col0 + i;
-                x += p.causal_alibi ? slope * static_cast<float>(col)
-                                    : -slope * fabsf(static_cast<float>(row + ti.off - col));
-              }
-              sr[i] = __float_as_uint(x);
+          // Scores leave this block already in the log2 domain.
+          const float inv_cap = (p.softcap > 0.f) ? p.scale / p.softcap : 0.f;
+          const float cap_l2 = p.softcap * 1.4426950408889634f;
+#pragma unroll
+          for (int i = 0; i < kBlockN; ++i) {
+            float x = __uint_as_float(sr[i]);
+            x = (p.softcap > 0.f) ? cap_l2 * tanh_approx(x * inv_cap) : x * p.scale_log2;
+            if (p.alibi != nullptr) {
+              const int col = col0 + i;
+              x += p.causal_alibi ? slope * static_cast<float>(col)
+                                  : -slope * fabsf(static_cast<float>(row + ti.off - col));
             }
-            cs = 1.f;
+            sr[i] = __float_as_uint(x);
           }
+          cs = 1.f;
           if (need_mask) {
             int hi = ti.sk;
             if (p.window_right >= 0) hi = min(hi, row + ti.off + p.window_right + 1);
@@ -360,21 +348,20 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             if (p.window_left >= 0) lo = row + ti.off - p.window_left;
             hi -= col0;
             lo -= col0;
-  #pragma unroll
+#pragma unroll
             for (int i = 0; i < kBlockN; ++i)
               if (i < lo || i >= hi) sr[i] = __float_as_uint(-INFINITY);
           }
           float mx0 = __uint_as_float(sr[0]), mx1 = __uint_as_float(sr[1]);
           float mx2 = __uint_as_float(sr[2]), mx3 = __uint_as_float(sr[3]);
-  #pragma unroll
+#pragma unroll
           for (int i = 4; i < kBlockN; i += 4) {
             mx0 = fmaxf(mx0, __uint_as_float(sr[i]));
             mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
             mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2]));
             mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
           }
-          const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * cs;
-          const float m_new = fmaxf(m, m_tile);
+          const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
           // Keep the stale max unless it grew by more than 2^8: the final O / l is exact either way.
           grow = (m_new - m) > kRescaleThreshold;
           if (grow) {
@@ -383,20 +370,10 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             l *= alpha;
           }
         }
-        bool waited;
-        if (j > nb_s) {
-          // P V(j-1) has to be complete: it reads the P buffer that this iteration overwrites, and it is the
-          // only operation that touches O of this stage.
-          waited = mbar_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitSoftmaxPvDone);
-        } else {
-          // First iteration of a tile: the TMA store of the previous tile must have read the buffer.
-          if (row_in == 0) {
-            tma_wait_group_read<0>();
-            mbar_arrive(&o_stage_free[s]);
-          }
-          waited = mbar_wait(&o_stage_free[s], n_first & 1, ctl, kWaitEpiFinal);
-          ++n_first;
-        }
+        // P V of the previous key tile (of this or of the previous work tile) has to be complete: it reads
+        // the P buffer that this iteration overwrites, and it is the only operation that touches O.
+        bool waited = true;
+        if (n_pv > 0) waited = mbar_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitSoftmaxPvDone);
         // One warp reduction reconverges the lanes after the wait and carries both warp-uniform
         // decisions: bit 1 = a lane's wait ran out, bit 0 = a lane's row maximum grew.
         const unsigned votes = __reduce_or_sync(0xffffffffu, (grow ? 1u : 0u) | (waited ? 0u : 2u));
@@ -416,12 +393,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           tmem_wait_st();
           tc_fence_before();
         }
-#ifdef FA2_TIMING
-        if (tm_on) FA2_STAMP(tm_base + 3);
-#endif
         if (!fancy) {
-          // ---- fast path: x = s * c - m with packed FMAs; kPolyPairs of every four pairs take their
-          // exponential on the FMA pipe, the others on the MUFU unit; packed row-sum accumulation.
+          // ---- fast path: x = s * c - m with packed FMAs, exp2 on the MUFU unit, packed row-sum accumulation.
           const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2);
           // A row that has seen no key yet has m = -inf and only -inf scores: keep x = -inf (not NaN).
           const float neg_m = (m == -INFINITY) ? 0.f : -m;
@@ -437,14 +410,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
               unpack_f32x2(v, x[2 * q], x[2 * q + 1]);
             }
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              if (q >= 4 - kPolyPairs) {
-                exp2_poly2(x[2 * q], x[2 * q + 1]);
-              } else {
-                x[2 * q] = ex2(x[2 * q]);
-                x[2 * q + 1] = ex2(x[2 * q + 1]);
-              }
-            }
+            for (int q = 0; q < 8; ++q) x[q] = ex2(x[q]);
             acc0 = add2(acc0, pack_f32x2(x[0], x[1]));
             acc1 = add2(acc1, pack_f32x2(x[2], x[3]));
             acc0 = add2(acc0, pack_f32x2(x[4], x[5]));
@@ -465,7 +431,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         } else {
           const float neg_m = (m == -INFINITY) ? 0.f : -m;
           float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-  #pragma unroll
+#pragma unroll
           for (int i = 0; i < kBlockN; i += 4) {
             const float p0 = ex2(fmaf(__uint_as_float(sr[i]), cs, neg_m));
             const float p1 = ex2(fmaf(__uint_as_float(sr[i + 1]), cs, neg_m));
@@ -479,94 +445,80 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             sr[i / 2 + 1] = pack2<BF16>(p2, p3);
           }
           l += (l0 + l1) + (l2 + l3);
-        }
-#ifdef FA2_TIMING
-        if (tm_on) FA2_STAMP(tm_base + 4);
-#endif
-        if (fancy) {
 #pragma unroll
           for (int c = 0; c < kBlockN / 8; ++c) store_p_chunk(c, sr[4 * c], sr[4 * c + 1], sr[4 * c + 2], sr[4 * c + 3]);
           fence_proxy_async_smem();
 #pragma unroll
           for (int q = 0; q < kPQ; ++q) mbar_arrive(&p_full[s * kPQ + q]);
         }
-#ifdef FA2_TIMING
-        if (tm_on) FA2_STAMP(tm_base + 5);
-#endif
         ++n_pv;
       }
       if (!ok) break;
-#ifdef FA2_TIMING
-      if (row_in == 0 && tm_tile < 16) FA2_STAMP(800 + tm_tile * 10 + 3 + s * 3);
-#endif
-      // ---- epilogue of this stage: O / l -> 16-bit -> swizzled smem -> one TMA store.
-      // A ragged tile of a packed batch (rows of the next sequence follow) uses predicated stores.
-      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o_ptr) + ti.bq * p.o_batch_stride +
-                       static_cast<int64_t>(ti.q_row0 + row) * p.o_row_stride + ti.h * p.o_head_stride;
-      const bool tma_store = (p.cu_q == nullptr) || (r_lo + kBlockM <= ti.sq);
-      if (ne_s > nb_s) {
-        if (!warp_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitEpiPvDone)) break;
-        tc_fence_after();
-        uint32_t orr[D];
+      // ---- end of the tile: hand (max, sum) of this row to the epilogue warps and go on.
+      if (!mbar_wait(&stat_free[s], (n_tile & 1) ^ 1, ctl, kWaitEpiFinal)) { ok = false; break; }
+      s_stat[s * kBlockM + row_in] = make_float2(m, l);
+      mbar_arrive(&stat_full[s]);
+      ++n_tile;
+    }
+    // The last P V of this stage: every commit on pv_done has landed before the CTA ends.
+    if (ok && n_pv > 0) mbar_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitSoftmaxPvDone);
+  } else if (warp < kMmaWarp) {
+    // ------------------------------------------------------------------ epilogue of both stages
+    reg_dealloc<kEpiRegs>();
+    const int row_in = tid - kEpiWarp * 32;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    uint32_t n_epi[2] = {0, 0};
+    bool ok = true;
+    for (int t = blockIdx.x; t - static_cast<int>(blockIdx.x) < p.num_tiles && ok; t += gridDim.x) {
+      const Tile ti = get_tile(p, t);
+      if (!ti.valid) continue;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) tmem_ld32(t_o + c * 32, orr + c * 32);
-        tmem_wait_ld();
-        tc_fence_before();
-        mbar_arrive(&o_free[s]);
-#ifdef FA2_TIMING
-        if (row_in == 0 && tm_tile < 16) FA2_STAMP(800 + tm_tile * 10 + 4 + s * 3);
-#endif
-        const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+      for (int s = 0; s < 2; ++s) {
+        const int row = ti.m0 + s * kBlockM + row_in;
+        const bool live = row < ti.sq;
+        uint16_t* orow = reinterpret_cast<uint16_t*>(p.o_ptr) + ti.bq * p.o_batch_stride +
+                         static_cast<int64_t>(ti.q_row0 + row) * p.o_row_stride + ti.h * p.o_head_stride;
+        float* lse_row = p.lse_ptr + ti.bq * p.lse_batch_stride + ti.h * p.lse_head_stride + ti.q_row0 + row;
+        if (ti.ne[s] > ti.nb[s]) {
+          const uint32_t par = n_epi[s] & 1;
+          const bool got = mbar_wait(&stat_full[s], par, ctl, kWaitEpiFinal) && mbar_wait(&o_full[s], par, ctl, kWaitEpiPvDone);
+          if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+          ++n_epi[s];
+          const float2 ml = s_stat[s * kBlockM + row_in];
+          mbar_arrive(&stat_free[s]);
+          const float inv_l = (ml.y > 0.f) ? 1.f / ml.y : 0.f;
+          const uint32_t t_o = tmem + lane_addr + (s == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
+          tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < D / 8; ++c) {  // 16-byte chunks of the row
-          uint4 w;
-          w.x = pack2<BF16>(__uint_as_float(orr[8 * c]) * inv_l, __uint_as_float(orr[8 * c + 1]) * inv_l);
-          w.y = pack2<BF16>(__uint_as_float(orr[8 * c + 2]) * inv_l, __uint_as_float(orr[8 * c + 3]) * inv_l);
-          w.z = pack2<BF16>(__uint_as_float(orr[8 * c + 4]) * inv_l, __uint_as_float(orr[8 * c + 5]) * inv_l);
-          w.w = pack2<BF16>(__uint_as_float(orr[8 * c + 6]) * inv_l, __uint_as_float(orr[8 * c + 7]) * inv_l);
-          if (tma_store) {
-            // chunk c lives in swizzle atom c / 8, at position (c % 8) ^ (row % 8) of the row's 128-byte line
-            *reinterpret_cast<uint4*>(stage_smem + (c / 8) * (kBlockM * 128) + row_in * 128 +
-                                      (((c & 7) ^ (row_in & 7)) << 4)) = w;
-          } else if (row < ti.sq && c * 8 < p.head_dim) {
-            *reinterpret_cast<uint4*>(orow + c * 8) = w;
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t orr[32];
+            tmem_ld32(t_o + c * 32, orr);
+            tmem_wait_ld();
+            if (c == D / 32 - 1) {
+              tc_fence_before();
+              mbar_arrive(&o_free[s]);  // the first P V of the stage's next tile may overwrite O
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {  // 16-byte chunks of the row
+              uint4 w;
+              w.x = pack2<BF16>(__uint_as_float(orr[8 * q]) * inv_l, __uint_as_float(orr[8 * q + 1]) * inv_l);
+              w.y = pack2<BF16>(__uint_as_float(orr[8 * q + 2]) * inv_l, __uint_as_float(orr[8 * q + 3]) * inv_l);
+              w.z = pack2<BF16>(__uint_as_float(orr[8 * q + 4]) * inv_l, __uint_as_float(orr[8 * q + 5]) * inv_l);
+              w.w = pack2<BF16>(__uint_as_float(orr[8 * q + 6]) * inv_l, __uint_as_float(orr[8 * q + 7]) * inv_l);
+              if (live && c * 32 + q * 8 < p.head_dim) *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = w;
+            }
           }
-        }
-        if (tma_store) {
-          fence_proxy_async_smem();
-          mbar_arrive(&epi_full[s]);
-          // A wait that runs out here sets the abort flag; the warp then leaves together at its next
-          // warp_wait, which is also where the lanes meet again after this single-lane section.
-          if (row_in == 0 && mbar_wait(&epi_full[s], n_store & 1, ctl, kWaitEpiFinal)) {
-#pragma unroll
-            for (int a = 0; a < Cfg::kAtoms; ++a)
-              if (a * 64 < p.head_dim)
-                tma_store_4d(&p.tm_o, stage_smem + a * (kBlockM * 128), a * 64, ti.h, ti.q_row0 + r_lo, ti.bq);
-            tma_commit_group();
-          }
-          ++n_store;
-        }
-      } else {
-        mbar_arrive(&o_free[s]);
-        if (row < ti.sq) {
-          // No key is visible to this stage: O = 0.
+          if (live) *lse_row = (ml.y > 0.f) ? (ml.x + lg2(ml.y)) * 0.6931471805599453f : INFINITY;
+        } else if (live) {
+          // No key is visible to this stage's rows: O = 0, LSE = +inf.
 #pragma unroll
           for (int q = 0; q < D / 8; ++q)
             if (q * 8 < p.head_dim) *reinterpret_cast<uint4*>(orow + q * 8) = make_uint4(0, 0, 0, 0);
+          *lse_row = INFINITY;
         }
+        __syncwarp();
       }
-#ifdef FA2_TIMING
-      if (row_in == 0 && tm_tile < 16) FA2_STAMP(800 + tm_tile * 10 + 5 + s * 3);
-      ++tm_tile;
-#endif
-      if (row < ti.sq) {
-        const float lse = (l > 0.f) ? (m + lg2(l)) * 0.6931471805599453f : INFINITY;
-        p.lse_ptr[ti.bq * p.lse_batch_stride + ti.h * p.lse_head_stride + ti.q_row0 + row] = lse;
-      }
-      // Rows past the end of a packed sequence skipped the stores above; the lanes meet again at the
-      // vote of the next warp_wait, before any aligned tcgen05 instruction.
     }
-    if (row_in == 0) tma_wait_group<0>();
   } else {
     reg_dealloc<kOtherRegs>();
     if (warp == kLoadWarp && lane == 0) {
@@ -610,13 +562,56 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           if (ok) ok = load_kv(&p.tm_v, ti.k_row0 + j * kBlockN, ti.hk, ti.bq);
         }
       }
-      if (!ok) {
-        // Give copies that are still in flight time to land before the CTA exits.
-        const long long t0 = clock64();
-        while (clock64() - t0 < 2000000) {
+      // The loader leaves last: it waits until the issuers' commits on every ring slot and on both Q stages
+      // have landed, so that no asynchronous arrival is still on its way when the CTA gives back its shared
+      // memory. A slot or stage that was never used passes at once.
+      for (int i = 0; i < Cfg::kSlots && ok; ++i) {
+        ok = mbar_wait(&kv_empty[slot], ring_phase ^ 1, ctl, kWaitLoadKVEmpty);
+        if (++slot == Cfg::kSlots) {
+          slot = 0;
+          ring_phase ^= 1;
         }
       }
-    } else if ((warp == kMmaWarp || warp == kMmaWarp1) && lane == 0) {
+      if (ok) ok = mbar_wait(&q_empty[0], (n_q0 & 1) ^ 1, ctl, kWaitLoadQEmpty);
+      if (ok) ok = mbar_wait(&q_empty[1], (n_q1 & 1) ^ 1, ctl, kWaitLoadQEmpty);
+    } else if (warp == kFixWarp) {
+      // ---------------------------------------------------------------- fixer (packed batches)
+      // Walks the ring in the loader's order and waits for every tile, which keeps it within one ring
+      // pass of the consumers; it acts on V tiles that reach past the end of their sequence.
+      if (packed) {
+        uint32_t slot = 0, ring_phase = 0;
+        bool ok = true;
+        auto step = [&](int first_stray) -> bool {
+          if (!__all_sync(0xffffffffu, mbar_wait(&kv_full[slot], ring_phase, ctl, kWaitMmaKVFull))) return false;
+          if (first_stray < kBlockN) {
+            uint8_t* tile = s_kv + slot * Cfg::kTileBytes;
+            // 8 lanes clear one 128-byte row of an atom (the swizzle only permutes 16-byte chunks inside it)
+            for (int r = first_stray + (lane >> 3); r < kBlockN; r += 4)
+#pragma unroll
+              for (int a = 0; a < Cfg::kAtoms; ++a)
+                *reinterpret_cast<uint4*>(tile + a * (kBlockN * 128) + r * 128 + (lane & 7) * 16) = make_uint4(0, 0, 0, 0);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&kv_fixed[slot]);
+            __syncwarp();
+          }
+          if (++slot == Cfg::kSlots) {
+            slot = 0;
+            ring_phase ^= 1;
+          }
+          return true;
+        };
+        for (int t = blockIdx.x; t - static_cast<int>(blockIdx.x) < p.num_tiles && ok; t += gridDim.x) {
+          const Tile ti = get_tile(p, t);
+          if (!ti.valid) continue;
+          if (ti.jlo < ti.jhi) ok = step(kBlockN);
+          for (int j = ti.jlo; j < ti.jhi && ok; ++j) {
+            if (j + 1 < ti.jhi) ok = step(kBlockN);
+            if (ok) ok = step(ragged_row(p, ti, j));
+          }
+        }
+      }
+    } else if ((warp == kMmaWarp || warp == kMmaWarp + 1) && lane == 0) {
       // ---------------------------------------------------------------- mma issuer
       // Descriptors are built once; inside the loops an operand address is one 64-bit add of a
       // compile-time constant (descriptor address field is in 16-byte units), so that the single
@@ -630,16 +625,15 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
       const uint64_t k_desc = make_smem_desc(smem_u32(s_kv), 16, 1024);                // K-major B
       const uint64_t v_desc = make_smem_desc(smem_u32(s_kv), kBlockN * 128, 1024);     // MN-major B
       // Each stage has its own issuing warp, and both walk the same sequence of tiles and K/V ring
-      // positions. A stage never waits for the other one: stage 0 may already run the next tile while
-      // stage 1 finishes the current one, and a piece of P V is issued while the other stage's
-      // exponentials are still in flight. A K/V slot is released by two commits, one per issuer.
-      const int s = (warp == kMmaWarp) ? 0 : 1;
+      // positions. A K/V slot is released by two commits, one per issuer.
+      const int s = warp - kMmaWarp;
       const uint64_t a_q = q_desc + s * kTile16;
       const uint32_t t_s = tmem + (s == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1);
       const uint32_t t_o = tmem + (s == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
-      const uint64_t a_p = make_smem_desc(smem_u32(s_o + s * Cfg::kStageBufBytes), 16, 1024);  // P: K-major A
+      const uint64_t a_p = make_smem_desc(smem_u32(s_p + s * Cfg::kPBytes), 16, 1024);  // P: K-major A
       uint32_t slot = 0, ring_phase = 0;  // K/V ring position of the next tile to consume
-      uint32_t n_qk = 0, n_p = 0, n_q = 0, n_tile = 0;
+      uint32_t fix_par = 0;               // bit i: parity of the next kv_fixed phase of slot i
+      uint32_t n_qk = 0, n_p = 0, n_q = 0, n_work = 0;
       bool ok = true;
       auto advance = [&]() {
         mma_commit(&kv_empty[slot]);
@@ -683,6 +677,11 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         // P row inside its swizzle atom, 16 rows of 128 bytes of V).
         auto do_v = [&](const int j) -> bool {
           if (!mbar_wait(&kv_full[slot], ring_phase, ctl, kWaitMmaKVFull)) return false;
+          if (ragged_row(p, ti, j) < kBlockN) {
+            // A V tile that reaches past its sequence is usable once the fixer has cleared the stray rows.
+            if (!mbar_wait(&kv_fixed[slot], (fix_par >> slot) & 1, ctl, kWaitMmaKVFull)) return false;
+            fix_par ^= 1u << slot;
+          }
           if (j >= nb && j < ne) {
             const bool first = (j == nb);
             const uint64_t b = v_desc + slot * kTile16;
@@ -690,7 +689,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
 #pragma unroll
             for (int q = 0; q < kPQ; ++q) {
               if (!mbar_wait(&p_full[s * kPQ + q], n_p & 1, ctl, kWaitMmaPFull)) return false;
-              if (q == 0 && first && !mbar_wait(&o_free[s], (n_tile & 1) ^ 1, ctl, kWaitMmaOFree)) return false;
+              if (q == 0 && first && !mbar_wait(&o_free[s], (n_work & 1) ^ 1, ctl, kWaitMmaOFree)) return false;
               tc_fence_after();
 #pragma unroll
               for (int ks = q * kStepsPerPiece; ks < (q + 1) * kStepsPerPiece; ++ks) {
@@ -701,6 +700,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             }
             ++n_p;
             mma_commit(&pv_done[s]);
+            if (j == ne - 1) mma_commit(&o_full[s]);  // the epilogue may read O_s
           }
           advance();
           return true;
@@ -710,7 +710,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           if (j + 1 < ti.jhi) ok = do_k(j + 1);
           if (ok) ok = do_v(j);
         }
-        ++n_tile;
+        if (ne > nb) ++n_work;
       }
     }
   }
@@ -725,14 +725,6 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == kMmaWarp) tmem_dealloc(tmem, 512);
-#ifdef FA2_TIMING
-  if (tid == 0 && blockIdx.x == 0) {
-    unsigned long long gt;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
-    g_fwd_timing[1002] = clock64();
-    g_fwd_timing[1003] = static_cast<long long>(gt);
-  }
-#endif
 }
 
 template <int D, bool BF16>
@@ -757,7 +749,7 @@ cudaError_t launch_one(const FwdParams& p, int num_sms, cudaStream_t stream) {
 
 cudaError_t launch_fwd(const FwdParams& p, int head_dim, bool bf16, int num_sms, cudaStream_t stream) {
   if (p.num_tiles <= 0) return cudaSuccess;
-  // Head dims below the kernel's D ride on TMA: loads past the real head dim read zeros, stores are clipped.
+  // Head dims below the kernel's D ride on TMA: loads past the real head dim read zeros; the epilogue's stores stop there.
   if (head_dim > 64 && head_dim <= 128) return bf16 ? launch_one<128, true>(p, num_sms, stream) : launch_one<128, false>(p, num_sms, stream);
   if (head_dim > 0 && head_dim <= 64) return bf16 ? launch_one<64, true>(p, num_sms, stream) : launch_one<64, false>(p, num_sms, stream);
   return cudaErrorInvalidValue;

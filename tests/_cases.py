@@ -22,3 +22,45 @@ def alibi_slopes(h):
 FWD_TOL = {torch.float16: dict(atol=2e-3, rtol=2.5e-2, mean=2e-3, lse=3e-2),
            torch.bfloat16: dict(atol=1e-2, rtol=5e-2, mean=8e-3, lse=8e-2)}
 BWD_TOL = {torch.float16: dict(atol=0.008, rtol=0.04), torch.bfloat16: dict(atol=0.06, rtol=0.08)}
+
+
+def sample_units(batch, heads, n=16):
+    """n (batch, head) pairs spread over both ends and the middle of the batch and head ranges."""
+    units = [(0, 0), (batch - 1, heads - 1), (0, heads - 1), (batch - 1, 0)]
+    g = torch.Generator().manual_seed(batch * 1000 + heads)
+    while len(units) < min(n, batch * heads):
+        u = (int(torch.randint(0, batch, (1,), generator=g)), int(torch.randint(0, heads, (1,), generator=g)))
+        if u not in units:
+            units.append(u)
+    return units
+
+
+def reference_class_kernel():
+    """The FA2 kernel family the reference's own gold test compares against
+    (flash-attn2-rs/tests/test_gold.py:8-9); on this image it is the flash_attn wheel. The reference
+    build itself (Rust + cuda-oxide) cannot run here, so this is the kernel whose error the
+    "no larger than twice the reference kernel's error" criterion is measured against. A GPU box
+    without it fails the test rather than skipping it."""
+    import pytest
+
+    try:
+        import flash_attn
+
+        return flash_attn
+    except Exception as e:  # noqa: BLE001
+        pytest.fail(f"the flash_attn stand-in for the reference kernel is not importable: {type(e).__name__}: {e}")
+
+
+# fp32 results (LSE) of two correct kernels differ by a few units in the last place of values of magnitude ~10,
+# whichever is "better" is noise: below this floor the factor of two is not applied.
+TWICE_FLOOR = {"lse": 1e-5}
+
+
+def assert_error_within_twice(name, ours, theirs, oracle):
+    """max|ours - oracle| <= 2 * max|theirs - oracle| (+ the fp32 noise floor for LSE)."""
+    ours, theirs, oracle = ours.float().cpu(), theirs.float().cpu(), oracle.float().cpu()
+    finite = torch.isfinite(oracle)
+    e_ours = (ours[finite] - oracle[finite]).abs().max().item()
+    e_theirs = (theirs[finite] - oracle[finite]).abs().max().item()
+    print(f"[2x] {name}: ours {e_ours:.3e} reference-class {e_theirs:.3e}")
+    assert e_ours <= max(2 * e_theirs, TWICE_FLOOR.get(name.split(":")[-1], 0.0)) + 1e-9, (name, e_ours, e_theirs)

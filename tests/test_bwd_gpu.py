@@ -144,7 +144,12 @@ def test_config3_full_size_slices_and_properties():
     assert ops.device_status() == 0
     for t in (dq, dk, dv):
         assert torch.isfinite(t.float()).all()
-    for b, h in [(0, 0), (9, 3), (15, 15)]:
+    from tests._cases import assert_error_within_twice, reference_class_kernel, sample_units
+
+    # the reference-class kernel's gradients on the same inputs, for the factor-of-two criterion
+    qa, ka, va = (t.clone().requires_grad_() for t in (qc, kc, vc))
+    reference_class_kernel().flash_attn_func(qa, ka, va, causal=True).backward(doc)
+    for b, h in sample_units(16, 16):
         sl = (slice(b, b + 1), slice(None), slice(h, h + 1))
         dq_ref, dk_ref, dv_ref, delta_ref = attention_backward(q[sl], k[sl], v[sl], do[sl], causal=True,
                                                                out=out[sl].float().cpu())
@@ -152,6 +157,12 @@ def test_config3_full_size_slices_and_properties():
         _close(dq[sl], dq_ref, torch.bfloat16, "dq")
         _close(dk[sl], dk_ref, torch.bfloat16, "dk")
         _close(dv[sl], dv_ref, torch.bfloat16, "dv")
+        # the oracle's gradients for the factor-of-two criterion use its own fp32 O (no kernel's rounding)
+        gq, gk, gv, _ = attention_backward(q[sl], k[sl], v[sl], do[sl], causal=True)
+        assert_error_within_twice("B16 H16 S2048 causal:dq", dq[sl], qa.grad[sl], gq)
+        assert_error_within_twice("B16 H16 S2048 causal:dk", dk[sl], ka.grad[sl], gk)
+        assert_error_within_twice("B16 H16 S2048 causal:dv", dv[sl], va.grad[sl], gv)
+    del qa, ka, va
     # key S-1 is visible to query S-1 only, with P = softmax weight p: dV[S-1] = p * dO[S-1]
     p_last = torch.exp((qc[:, -1].float() * kc[:, -1].float()).sum(-1) / 128 ** 0.5 - lse[:, :, -1])
     torch.testing.assert_close(dv[:, -1].float(), p_last.unsqueeze(-1) * doc[:, -1].float(), atol=2e-3, rtol=2e-2)
@@ -256,3 +267,49 @@ def test_dq_only_call_is_bit_reproducible(causal):
     dq_ref, _, _, _ = attention_backward(q[sl], k[:, :, 1:2][1:2], v[:, :, 1:2][1:2], do[sl], causal=causal,
                                          out=out[sl].float().cpu())
     _close(runs[0][sl], dq_ref, torch.bfloat16, "dq")
+
+
+TWICE_BWD_CASES = [
+    ("B2 H4 S1024 D128 bf16 causal", (2, 4, 4, 1024, 1024, 128), torch.bfloat16, True),
+    ("B2 H8/2 S512 D128 f16 causal", (2, 8, 2, 512, 512, 128), torch.float16, True),
+    ("B1 H4 S640 D64 bf16 full", (1, 4, 4, 640, 640, 64), torch.bfloat16, False),
+]
+
+
+@pytest.mark.parametrize("name,shape,dtype,causal", TWICE_BWD_CASES, ids=[c[0] for c in TWICE_BWD_CASES])
+def test_gradient_error_no_larger_than_twice_a_reference_class_kernel(name, shape, dtype, causal):
+    """dQ, dK, dV: max|err| against the fp32 oracle must be <= 2x that of an FA2 kernel of the reference's
+    family on the same inputs (tests/_cases.py: reference_class_kernel), each kernel differentiating its
+    own forward."""
+    from oracle.attention_oracle import attention_backward
+    from tests._cases import assert_error_within_twice, reference_class_kernel
+
+    b, h, hk, sq, sk, d = shape
+    q, k, v, do = make_qkv(2, b, h, hk, sq, sk, d, dtype, with_do=True)
+    _, _, _, dq, dk, dv = _run(q, k, v, do, causal=causal)
+    qa, ka, va = (t.cuda().requires_grad_() for t in (q, k, v))
+    reference_class_kernel().flash_attn_func(qa, ka, va, causal=causal).backward(do.cuda())
+    gq, gk, gv, _ = attention_backward(q, k, v, do, causal=causal)
+    assert_error_within_twice(name + ":dq", dq, qa.grad, gq)
+    assert_error_within_twice(name + ":dk", dk, ka.grad, gk)
+    assert_error_within_twice(name + ":dv", dv, va.grad, gv)
+
+
+@pytest.mark.parametrize("causal", [True, False], ids=["causal", "full"])
+def test_ordered_dq_with_more_key_blocks_than_sms(causal):
+    """A dQ-only call adds the key blocks of a head in a fixed order, each waiting for the ones before it.
+    With more key blocks than the GPU has SMs (160 here) the blocks waited for must already be running:
+    the grid lists them in the order of their turns. The status word must stay clean, repeated runs
+    must agree bit for bit, and the result must match the call that adds in arrival order."""
+    from flash_attn2_b200 import cabi_ops as ops
+
+    s = 160 * 128
+    q, k, v, do = [t.cuda() for t in make_qkv(13, 1, 1, 1, s, s, 64, torch.bfloat16, with_do=True)]
+    out, lse = ops.fwd(q, k, v, causal=causal)
+    delta = ops.bwd_preprocess(do, out)
+    a = ops.bwd(q, k, v, do, lse, delta, causal=causal, which=1)[0]
+    b = ops.bwd(q, k, v, do, lse, delta, causal=causal, which=1)[0]
+    assert ops.device_status() == 0
+    assert torch.equal(a, b)
+    free = ops.bwd(q, k, v, do, lse, delta, causal=causal, which=3)[0]
+    torch.testing.assert_close(a.float(), free.float(), atol=2e-2, rtol=2e-2)

@@ -109,11 +109,13 @@ def test_varlen_through_tvm_ffi_ops():
 
 
 def test_config4_full_size():
-    """BASELINE configs[3]: 32 sequences, lengths U[128, 4096] from seed 3, H 32/8, D 128, causal.
-    Oracle on three whole sequences (all heads of one KV group), dense-vs-packed equality on one
-    sequence, finiteness and +inf-free LSE everywhere."""
+    """32 packed sequences, lengths U[128, 4096] from seed 3, H 32/8, D 128, causal, bf16, forward and
+    backward from ONE launch of each kernel. Oracle on three whole sequences (all heads of one KV group)
+    for O, LSE, dQ, dK, dV, the factor-of-two criterion against the reference-class kernel on the same
+    sequences, dense-vs-packed equality on one sequence, finiteness and +inf-free LSE everywhere."""
     from flash_attn2_b200 import cabi_ops as ops
-    from oracle.attention_oracle import attention_forward
+    from oracle.attention_oracle import attention_backward, attention_forward
+    from tests._cases import assert_error_within_twice, reference_class_kernel
 
     g = torch.Generator().manual_seed(3)
     lengths = torch.randint(128, 4097, (32,), generator=g).tolist()
@@ -126,12 +128,37 @@ def test_config4_full_size():
     out, lse = ops.varlen_fwd(qc, kc, vc, cc, cc, max(lengths), max(lengths), causal=True)
     assert ops.device_status() == 0
     assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    do = torch.randn(total, 32, 128, generator=g).to(torch.bfloat16)
+    doc = do.cuda()
+    delta = ops.bwd_preprocess(doc, out, cu_seqlens_q=cc, max_seqlen_q=max(lengths))
+    dq, dk, dv = ops.bwd(qc, kc, vc, doc, lse, delta, cu_seqlens_q=cc, cu_seqlens_k=cc, max_seqlen_q=max(lengths),
+                         max_seqlen_k=max(lengths), causal=True)
+    assert ops.device_status() == 0
+    for t in (dq, dk, dv):
+        assert torch.isfinite(t.float()).all()
+    fa = reference_class_kernel()
+    qa, ka, va = (t.clone().requires_grad_() for t in (qc, kc, vc))
+    theirs, their_lse, _ = fa.flash_attn_varlen_func(qa, ka, va, cc, cc, max(lengths), max(lengths), causal=True,
+                                                     return_attn_probs=True)
+    theirs.backward(doc)
+    tol = BWD_TOL[torch.bfloat16]
     order = sorted(range(32), key=lambda i: lengths[i])
     for i in (order[0], order[15], order[-1]):  # shortest, median, longest
         a, b = int(cu[i]), int(cu[i + 1])
-        o_ref, lse_ref = attention_forward(q[a:b, 4:8].unsqueeze(0), k[a:b, 1:2].unsqueeze(0),
-                                           v[a:b, 1:2].unsqueeze(0), causal=True)
-        _fwd_close(out[a:b, 4:8].unsqueeze(0), lse[4:8, a:b].unsqueeze(0), o_ref, lse_ref, torch.bfloat16)
+        sl_q, sl_k = (slice(a, b), slice(4, 8)), (slice(a, b), slice(1, 2))
+        o_ref, lse_ref = attention_forward(q[sl_q].unsqueeze(0), k[sl_k].unsqueeze(0), v[sl_k].unsqueeze(0), causal=True)
+        _fwd_close(out[sl_q].unsqueeze(0), lse[4:8, a:b].unsqueeze(0), o_ref, lse_ref, torch.bfloat16)
+        assert_error_within_twice("packed H32/8 causal:out", out[sl_q], theirs[sl_q].detach(), o_ref[0])
+        # the stand-in returns LSE as [H, total_q] for packed input
+        assert_error_within_twice("packed H32/8 causal:lse", lse[4:8, a:b], their_lse[4:8, a:b], lse_ref[0])
+        # dK / dV of kv head 1 sum over its four query heads 4..7: this group is complete
+        gq, gk, gv, _ = attention_backward(q[sl_q].unsqueeze(0), k[sl_k].unsqueeze(0), v[sl_k].unsqueeze(0),
+                                           do[sl_q].unsqueeze(0), causal=True)
+        for name, got, ref, their in (("dq", dq[sl_q], gq[0], qa.grad[sl_q]), ("dk", dk[sl_k], gk[0], ka.grad[sl_k]),
+                                      ("dv", dv[sl_k], gv[0], va.grad[sl_k])):
+            torch.testing.assert_close(got.float().cpu(), ref, atol=tol["atol"], rtol=tol["rtol"])
+            assert_error_within_twice("packed H32/8 causal:" + name, got, their, ref)
+    del qa, ka, va, theirs
     i = order[20]
     a, b = int(cu[i]), int(cu[i + 1])
     dense, dense_lse = ops.fwd(qc[a:b].unsqueeze(0), kc[a:b].unsqueeze(0), vc[a:b].unsqueeze(0), causal=True)
@@ -165,3 +192,43 @@ def test_varlen_other_head_dim_ragged():
     for got, ref in ((dq, dq_ref), (dk, dk_ref), (dv, dv_ref)):
         torch.testing.assert_close(got.float().cpu(), ref, atol=tol["atol"], rtol=tol["rtol"])
     assert (guard == 7.0).all()
+
+
+def test_rows_after_a_packed_sequence_do_not_leak():
+    """The reference zero-fills the rows of a tile that lie past the end of a sequence
+    (flash-attn2-rs/src/device/forward/mod.rs:171-175,200), so what a neighbouring sequence holds can
+    never reach this one. Here every second sequence of the batch is filled with NaN (Q, K, V, dO):
+    the outputs and gradients of the clean sequences must equal, bit for bit, those of a batch whose
+    other sequences hold ordinary numbers (dQ, which is summed in arrival order, within tolerance)."""
+    from flash_attn2_b200 import cabi_ops as ops
+
+    lengths = [130, 77, 257, 40, 300, 64]
+    q, k, v, cu, _, do = _packed(5, lengths, lengths, 4, 2, 128, torch.bfloat16, with_do=True)
+    cc = cu.cuda()
+    clean = [0, 2, 4]
+
+    def run(poison):
+        ts = [t.clone() for t in (q, k, v, do)]
+        if poison:
+            for i in (1, 3, 5):
+                for t in ts:
+                    t[int(cu[i]):int(cu[i + 1])] = float("nan")
+        qc, kc, vc, doc = [t.cuda() for t in ts]
+        out, lse = ops.varlen_fwd(qc, kc, vc, cc, cc, max(lengths), max(lengths), causal=True)
+        delta = ops.bwd_preprocess(doc, out, cu_seqlens_q=cc, max_seqlen_q=max(lengths))
+        dq, dk, dv = ops.bwd(qc, kc, vc, doc, lse, delta, cu_seqlens_q=cc, cu_seqlens_k=cc,
+                             max_seqlen_q=max(lengths), max_seqlen_k=max(lengths), causal=True)
+        assert ops.device_status() == 0
+        return out, lse, dq, dk, dv
+
+    base, bad = run(False), run(True)
+    for i in clean:
+        a, b = int(cu[i]), int(cu[i + 1])
+        for name, x, y in zip(("out", "dq", "dk", "dv"), (base[0], base[2], base[3], base[4]),
+                              (bad[0], bad[2], bad[3], bad[4])):
+            assert torch.isfinite(y[a:b].float()).all(), (name, i)
+            if name == "dq":
+                torch.testing.assert_close(y[a:b].float(), x[a:b].float(), atol=2e-2, rtol=2e-2)
+            else:
+                assert torch.equal(x[a:b], y[a:b]), (name, i)
+        assert torch.equal(base[1][:, a:b], bad[1][:, a:b])
