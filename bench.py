@@ -34,7 +34,11 @@ CAUSAL = True
 FWD_FLOPS = 4.0 * B * H * S * S * D * 0.5
 BWD_FLOPS = 2.5 * FWD_FLOPS
 METRIC = "FA2 fwd/bwd TFLOP/s bf16 B16 H16 S2048 D128 causal; % of B200 dense peak"
-WORKLOAD = "FA2 forward+backward, causal, B=16, H_q=H_kv=16, S=2048, D=128, bf16 (BASELINE configs[1]+[2])"
+WORKLOAD = "FA2 forward+backward, causal, B=16, H_q=H_kv=16, S=2048, D=128, bf16"
+# Long-context leg (strong scaling): one seeded tensor, heads split over the ranks.
+LC_S, LC_H = 16384, 32
+LC_FWD_FLOPS = 4.0 * LC_H * LC_S * LC_S * D * 0.5
+LC_BWD_FLOPS = 2.5 * LC_FWD_FLOPS
 
 
 def measured_peaks():
@@ -141,6 +145,63 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_long_context(ops, dev, rank, world, timed, steps):
+    """B=1, H=32, S=16384, D=128, bf16, causal, seed 4: rank r of N runs heads shard_heads(32, 32, N, r) as
+    strided views of the one seeded tensor (fixed total work: strong scaling, no collective in the timed
+    region). Afterwards, once, the shards of O, LSE, dQ, dK, dV are all-gathered (NCCL) and rank 0 compares
+    them with its own unsharded run."""
+    import torch.distributed as dist
+    from flash_attn2_b200.sharding import gather_shards, shard_heads
+
+    if LC_H % world:
+        return {"skipped": f"{LC_H} heads do not split over {world} ranks"}
+    g = torch.Generator().manual_seed(4)
+    full = [torch.randn(1, LC_S, LC_H, D, generator=g).to(torch.bfloat16).to(dev) for _ in range(4)]
+    hq, hkv = shard_heads(LC_H, LC_H, world, rank)
+    q, k, v, do = [t[:, :, hq] for t in full]
+    acc = torch.empty(LC_S * (hq.stop - hq.start) * D, dtype=torch.float32, device=dev)
+    state = {}
+
+    def fwd():
+        state["o"], state["lse"] = ops.fwd(q, k, v, causal=True)
+
+    def bwd():
+        delta = ops.bwd_preprocess(do, state["o"])
+        state["g"] = ops.bwd(q, k, v, do, state["lse"], delta, causal=True, dq_accum=acc)
+
+    for _ in range(3):
+        fwd()
+        bwd()
+    ms_f = timed(fwd, steps)
+    ms_b = timed(bwd, steps)
+    res = {"workload": f"FA2 forward+backward, causal, B=1, H_q=H_kv={LC_H}, S={LC_S}, D={D}, bf16, seed 4",
+           "scaling": "strong", "sharding": f"{LC_H // world} heads per GPU, strided views of the full tensors",
+           "fwd_ms": ms_f, "bwd_ms": ms_b, "fwd_tflops": LC_FWD_FLOPS / ms_f / 1e9, "bwd_tflops": LC_BWD_FLOPS / ms_b / 1e9,
+           "tflops": (LC_FWD_FLOPS + LC_BWD_FLOPS) / (ms_f + ms_b) / 1e9}
+    # verification, outside every timed region
+    dq, dk, dv = state["g"]
+    shards = {"out": (state["o"], 2), "lse": (state["lse"], 1), "dq": (dq, 2), "dk": (dk, 2), "dv": (dv, 2)}
+    if world > 1:
+        gathered = {n: gather_shards(t, dim) for n, (t, dim) in shards.items()}
+    else:
+        gathered = {n: t for n, (t, _) in shards.items()}
+    if rank == 0:
+        o, lse = ops.fwd(*full[:3], causal=True)
+        delta = ops.bwd_preprocess(full[3], o)
+        ref = dict(zip(("dq", "dk", "dv"), ops.bwd(*full, lse, delta, causal=True)), out=o, lse=lse)
+        verify = {}
+        for n, t in gathered.items():
+            if torch.equal(t, ref[n]):
+                verify[n] = "bit-identical"
+            else:
+                verify[n] = "max abs diff %.3e" % (t.float() - ref[n].float()).abs().max().item()
+        res["gathered_vs_unsharded"] = verify
+        res["gather"] = "NCCL all_gather of the head shards" if world > 1 else "single rank"
+    if world > 1:
+        dist.barrier()
+    return res
+
+
 def run_ours(args, rank, world):
     import torch.distributed as dist
     from flash_attn2_b200 import cabi_ops as ops
@@ -160,10 +221,14 @@ def run_ours(args, rank, world):
     k0.record(), k1.record()  # materialise the handles
     torch.cuda.synchronize()
 
+    launches = {"n": 0}  # kernels of this library enqueued: forward 1, delta preprocess 1, backward 2 (dQ/dK/dV + dQ convert)
+
     def fwd_only():
+        launches["n"] += 1
         return ops.fwd(q, k, v, causal=CAUSAL)
 
     def bwd_only(o, lse, events=None):
+        launches["n"] += 3
         delta = ops.bwd_preprocess(do, o)
         return ops.bwd(q, k, v, do, lse, delta, causal=CAUSAL, dq_accum=acc, kernel_events=events)
 
@@ -195,7 +260,9 @@ def run_ours(args, rank, world):
     for _ in range(args.warmup):
         step()
     with ClockSampler(local) as clocks:
+        launches["n"] = 0
         ms_step = timed(step, args.steps)
+        launches_timed = launches["n"]
         # Per-kernel figures for the roofline and the per-pass targets.
         ms_fwd = timed(fwd_only, args.steps)
         o, lse = fwd_only()
@@ -209,6 +276,19 @@ def run_ours(args, rank, world):
     status = ops.device_status()
     if status != 0:
         raise RuntimeError(f"kernel pipeline reported a stalled wait (status {status})")
+
+    # Sustained leg: the same step back to back for at least a second, so that the GPU settles at the clock
+    # its power limit allows; reported beside the burst figure with its own clock record.
+    sustained = None
+    if not args.kernels_only:
+        n_sus = max(args.steps, int(1100.0 / ms_step) + 1)
+        with ClockSampler(local) as sus_clocks:
+            ms_sus = timed(step, n_sus)
+        sustained = {"steps": n_sus, "ms_per_step": ms_sus, "clocks": sus_clocks.summary()}
+
+    long_context = None
+    if not args.kernels_only and args.batch == 16:
+        long_context = run_long_context(ops, dev, rank, world, timed, max(3, args.steps // 2))
 
     # End to end through the operator (plugin) API with host buffers: H2D of q, k, v, dO, the
     # tvm-ffi forward + backward, D2H of O, LSE, dQ, dK, dV.
@@ -285,7 +365,7 @@ def run_ours(args, rank, world):
         ms_e2e = timed_pipeline(e2e_steps)
 
     if rank == 0:
-        peak, sustained, peak_kind = measured_peaks()
+        peak, peak_sustained, peak_kind = measured_peaks()
         total = (FWD_FLOPS + BWD_FLOPS) * world
         tf = lambda fl, ms: fl / ms / 1e9  # noqa: E731
         traffic = None
@@ -303,16 +383,24 @@ def run_ours(args, rank, world):
                    "sample": f"{pairs} of the {B * H} (batch, head) units, forward + backward, fp32 on the host CPU"}
         achieved = tf(BWD_FLOPS, ms_bwd_kernel)
         line = {
-            "metric": METRIC, "value": tf(total, ms_step), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "metric": METRIC if B == 16 else METRIC.replace("B16", f"B{B}") + " (reduced batch)",
+            "value": tf(total, ms_step), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "global_batch": B * world, "sharding": "independent batches per GPU",
-                       "l2": "inputs and outputs (1.1 GB per step) exceed the 126 MB L2"},
+            "config": {"workload": WORKLOAD if B == 16 else WORKLOAD.replace("B=16", f"B={B}") + " (reduced batch: not the headline configuration)",
+                       "global_batch": B * world, "sharding": "independent batches per GPU",
+                       "l2": "inputs and outputs (1.1 GB per step at B=16) exceed the 126 MB L2",
+                       "value_path": "C ABI (fa2_fwd, fa2_bwd_preprocess, fa2_bwd) with a preallocated dQ accumulator, inputs resident in HBM",
+                       "e2e_path": "tvm-ffi operators (fwd_lse, bwd_preprocess, bwd_all) with pinned host buffers"},
             "detail": {
                 "fwd_tflops": tf(FWD_FLOPS * world, ms_fwd), "bwd_tflops": tf(BWD_FLOPS * world, ms_bwd),
                 "fwd_ms": ms_fwd, "bwd_ms": ms_bwd, "bwd_kernel_ms": ms_bwd_kernel,
                 "fwd_frac_of_peak": tf(FWD_FLOPS, ms_fwd) / peak, "bwd_frac_of_peak": tf(BWD_FLOPS, ms_bwd) / peak,
-                "peak_tflops": peak, "peak_sustained_tflops": sustained, "peak_kind": peak_kind,
+                "peak_tflops": peak, "peak_sustained_tflops": peak_sustained, "peak_kind": peak_kind,
+                "sustained": None if sustained is None else dict(
+                    sustained, tflops=tf(total, sustained["ms_per_step"]),
+                    frac_of_sustained_peak=None if not peak_sustained else tf(total / world, sustained["ms_per_step"]) / peak_sustained),
+                "long_context": long_context,
             },
             "roofline": {"kernel": "bwd_kernel<128, bf16>", "bound": "tensor", "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind},
@@ -322,7 +410,7 @@ def run_ours(args, rank, world):
             "e2e": None if ms_e2e is None else {"value": tf(total, ms_e2e), "unit": "TFLOP/s",
                                                  "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
                                                  "ms_per_step": ms_e2e},
-            "gpu_launches": 4 * args.steps,
+            "gpu_launches": launches_timed,
             "clocks": clocks.summary(),
         }
         print(json.dumps(line), flush=True)

@@ -22,55 +22,70 @@ __device__ __forceinline__ float2 unpack2(uint32_t w) {
   }
 }
 
-// One group of LANES threads per (batch, row, head); each thread reads 16 bytes at a time.
-// Rows are enumerated over the padded length so the padding is written as zero.
+// One group of LANES threads handles kRows consecutive (batch, row, head) units; each thread reads 16 bytes
+// of dO and of O per unit, and all of a thread's loads are issued before the first is used, which keeps
+// enough bytes in flight to run at HBM speed. Rows are enumerated over the padded length so the padding
+// is written as zero.
+constexpr int kRows = 4;
+
 template <bool BF16, int LANES>
 __global__ void __launch_bounds__(256) preprocess_kernel(const PreprocessParams p) {
-  const int64_t gid = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) / LANES;
+  const int64_t group = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) / LANES;
   const int lane = threadIdx.x % LANES;
   const int64_t total = static_cast<int64_t>(p.batch) * p.seqlen_pad * p.heads;
-  // No thread leaves before the shuffles below: a warp holds 32 / LANES groups, which may belong to
-  // different (batch, row) units when the head count is odd.
-  const bool in_range = gid < total;
-  const int h = static_cast<int>((in_range ? gid : 0) % p.heads);
-  const int64_t bs = (in_range ? gid : 0) / p.heads;
-  const int s = static_cast<int>(bs % p.seqlen_pad);
-  const int b = static_cast<int>(bs / p.seqlen_pad);
-  int64_t row = s;     // row inside the input tensors
-  int64_t drow = s;    // row inside delta
-  bool live = in_range && s < p.seqlen_q;
-  bool store = in_range;
-  int bq = b;
-  if (p.cu_q != nullptr) {
-    const int q0 = p.cu_q[b];
-    const int len = p.cu_q[b + 1] - q0;
-    live = in_range && s < len;
-    row = q0 + s;
-    drow = q0 + 128 * b + s;
-    bq = 0;
-    // Padding of a packed sequence: only the 128-row tail that belongs to it.
-    if (s >= (len + 127) / 128 * 128) store = false;
-  }
-  float sum = 0.f;
-  if (live) {
-    const uint4* a = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.dout) + bq * p.do_batch_stride +
-                                                    row * p.do_row_stride + h * p.do_head_stride);
-    const uint4* o = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.out) + bq * p.o_batch_stride +
-                                                    row * p.o_row_stride + h * p.o_head_stride);
-    for (int i = lane; i < p.head_dim / 8; i += LANES) {
-      const uint4 x = a[i], y = o[i];
-      const uint32_t xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+  const int chunks = p.head_dim / 8;  // 16-byte chunks per row; LANES >= chunks
+  uint4 x[kRows], y[kRows];
+  bool store[kRows];
+  int64_t dst[kRows];
+  // No thread leaves before the shuffles below: a warp holds 32 / LANES groups, some of which may lie past
+  // the end.
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 fx = unpack2<BF16>(xs[k]), fy = unpack2<BF16>(ys[k]);
-        sum = fmaf(fx.x, fy.x, sum);
-        sum = fmaf(fx.y, fy.y, sum);
-      }
+  for (int r = 0; r < kRows; ++r) {
+    const int64_t gid = group * kRows + r;
+    const bool in_range = gid < total;
+    const int h = static_cast<int>((in_range ? gid : 0) % p.heads);
+    const int64_t bs = (in_range ? gid : 0) / p.heads;
+    const int s = static_cast<int>(bs % p.seqlen_pad);
+    const int b = static_cast<int>(bs / p.seqlen_pad);
+    int64_t row = s;     // row inside the input tensors
+    int64_t drow = s;    // row inside delta
+    bool live = in_range && s < p.seqlen_q;
+    store[r] = in_range;
+    int bq = b;
+    if (p.cu_q != nullptr) {
+      const int q0 = p.cu_q[b];
+      const int len = p.cu_q[b + 1] - q0;
+      live = in_range && s < len;
+      row = q0 + s;
+      drow = q0 + 128 * b + s;
+      bq = 0;
+      // Padding of a packed sequence: only the 128-row tail that belongs to it.
+      if (s >= (len + 127) / 128 * 128) store[r] = false;
+    }
+    dst[r] = bq * p.delta_batch_stride + h * p.delta_head_stride + drow;
+    x[r] = make_uint4(0, 0, 0, 0);
+    y[r] = make_uint4(0, 0, 0, 0);
+    if (live && lane < chunks) {
+      x[r] = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.dout) + bq * p.do_batch_stride +
+                                            row * p.do_row_stride + h * p.do_head_stride)[lane];
+      y[r] = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.out) + bq * p.o_batch_stride +
+                                            row * p.o_row_stride + h * p.o_head_stride)[lane];
     }
   }
 #pragma unroll
-  for (int d = LANES / 2; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d, LANES);
-  if (lane == 0 && store) p.delta[bq * p.delta_batch_stride + h * p.delta_head_stride + drow] = sum;
+  for (int r = 0; r < kRows; ++r) {
+    const uint32_t xs[4] = {x[r].x, x[r].y, x[r].z, x[r].w}, ys[4] = {y[r].x, y[r].y, y[r].z, y[r].w};
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 fx = unpack2<BF16>(xs[k]), fy = unpack2<BF16>(ys[k]);
+      sum = fmaf(fx.x, fy.x, sum);
+      sum = fmaf(fx.y, fy.y, sum);
+    }
+#pragma unroll
+    for (int d = LANES / 2; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d, LANES);
+    if (lane == 0 && store[r]) p.delta[dst[r]] = sum;
+  }
 }
 
 template <bool BF16>
@@ -98,17 +113,20 @@ __global__ void __launch_bounds__(256) dq_convert_kernel(const float4* __restric
 }  // namespace
 
 cudaError_t launch_bwd_preprocess(const PreprocessParams& p, cudaStream_t stream) {
-  const int64_t groups = static_cast<int64_t>(p.batch) * p.seqlen_pad * p.heads;
-  if (groups == 0) return cudaSuccess;
-  const int lanes = p.head_dim <= 64 ? 8 : 16;
+  const int64_t units = static_cast<int64_t>(p.batch) * p.seqlen_pad * p.heads;
+  if (units == 0) return cudaSuccess;
+  const int64_t groups = (units + kRows - 1) / kRows;
+  const int lanes = p.head_dim <= 64 ? 8 : p.head_dim <= 128 ? 16 : 32;  // one 16-byte chunk of the row per lane
   const int64_t threads = groups * lanes;
   const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
   if (p.bf16) {
     if (lanes == 8) preprocess_kernel<true, 8><<<grid, 256, 0, stream>>>(p);
-    else preprocess_kernel<true, 16><<<grid, 256, 0, stream>>>(p);
+    else if (lanes == 16) preprocess_kernel<true, 16><<<grid, 256, 0, stream>>>(p);
+    else preprocess_kernel<true, 32><<<grid, 256, 0, stream>>>(p);
   } else {
     if (lanes == 8) preprocess_kernel<false, 8><<<grid, 256, 0, stream>>>(p);
-    else preprocess_kernel<false, 16><<<grid, 256, 0, stream>>>(p);
+    else if (lanes == 16) preprocess_kernel<false, 16><<<grid, 256, 0, stream>>>(p);
+    else preprocess_kernel<false, 32><<<grid, 256, 0, stream>>>(p);
   }
   return cudaGetLastError();
 }

@@ -26,8 +26,11 @@
 #include "fa2_params.h"
 #include "fa2_launch.h"
 
-namespace fa2 {
+#ifndef FA2_BWD_EARLY_S
+#define FA2_BWD_EARLY_S 1
+#endif
 
+namespace fa2 {
 
 namespace {
 
@@ -337,6 +340,18 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           });
         }
         mma_commit(&do_empty[st]);
+#if FA2_BWD_EARLY_S
+        // S^T of the next iteration, right behind dV: the tensor pipe executes in issue order, so dV has read
+        // P^T before these MMAs overwrite the columns, and the compute warps find the next scores ready when
+        // they finish dS^T instead of waiting for dQ and S^T after it.
+        if (has_next) {
+          ok = q_ready(it + 1, st ^ 1, nph, kWaitBwd + 8);
+          if (!ok) break;
+          tc_fence_after();
+          kmajor_pair(tmem + Cfg::kTmemS, k_kmaj, q_kmaj + (st ^ 1) * kTile16);
+          mma_commit(s_full);
+        }
+#endif
         // dQ = dS K   (into the dP^T columns, which the compute warps have drained)
         ok = mbar_wait(ds_full, it & 1, ctl, kWaitBwd + 7);
         if (!ok) break;
@@ -348,6 +363,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           });
           mma_commit(dq_full);
         }
+#if !FA2_BWD_EARLY_S
         // S^T of the next iteration
         if (has_next) {
           ok = q_ready(it + 1, st ^ 1, nph, kWaitBwd + 8);
@@ -356,6 +372,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           kmajor_pair(tmem + Cfg::kTmemS, k_kmaj, q_kmaj + (st ^ 1) * kTile16);
           mma_commit(s_full);
         }
+#endif
         // dK += dS^T Q
         {
           const uint64_t b = q_mn + st * kTile16;
@@ -630,6 +647,13 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(dq_free);
+        // Packed batches: the 32-row boxes of the reduce-adds below reach past the end of the sequence into
+        // the next sequence's rows. Rows past the end hold nothing of this sequence (and possibly NaN, when this
+        // sequence's own data is not finite): they add exact zeros.
+        if (p.cu_q != nullptr && m0 + (warp & 3) * 32 + lane >= ti.sq) {
+#pragma unroll
+          for (int i = 0; i < D; ++i) acc[i] = 0u;
+        }
         // Each warp drains its own 32 rows: pieces of 32 fp32 columns (4 KB) roll through the warp's share
         // of the stage (two buffers at D = 128). Piece k is staged as soon as the reduce of piece k - kBufs
         // has read its buffer, so the reduce engine always has a piece queued, and nothing but the warp

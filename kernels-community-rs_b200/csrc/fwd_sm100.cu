@@ -55,9 +55,17 @@ constexpr int kEpiWarp = 8;    // first warp of the epilogue warpgroup
 constexpr int kMmaWarp = 12;   // issues the MMAs of stage 0 (warp 13: stage 1); owns the TMEM allocation
 constexpr int kLoadWarp = 14;
 constexpr int kFixWarp = 15;
-constexpr int kSoftmaxRegs = 184;
-constexpr int kEpiRegs = 64;
-constexpr int kOtherRegs = 80;
+// Registers per thread after the warpgroups have traded them (setmaxnreg): 2 x 128 x 184 + 128 x 64 + 128 x 80
+// = 65536, the whole register file.
+#ifndef FA2_FWD_REGS_S
+#define FA2_FWD_REGS_S 184
+#define FA2_FWD_REGS_E 64
+#define FA2_FWD_REGS_O 80
+#endif
+constexpr int kSoftmaxRegs = FA2_FWD_REGS_S;
+constexpr int kEpiRegs = FA2_FWD_REGS_E;
+constexpr int kOtherRegs = FA2_FWD_REGS_O;
+static_assert(2 * kSoftmaxRegs + kEpiRegs + kOtherRegs <= 512, "the four warpgroups share 64 K registers");
 constexpr int kPQ = FA2_PQ;                // P is handed to the MMA warp in kPQ pieces of kBlockN / kPQ keys
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain
 
