@@ -26,10 +26,6 @@
 #include "fa2_params.h"
 #include "fa2_launch.h"
 
-#ifndef FA2_BWD_EARLY_S
-#define FA2_BWD_EARLY_S 1
-#endif
-
 namespace fa2 {
 
 namespace {
@@ -53,9 +49,10 @@ struct BwdCfg {
   static constexpr int kDSBytes = kBlk * kBlk * 2;
   static constexpr int kBarOff = kDSOff + kDSBytes;
   static constexpr int kNumBars = 26;
-  static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+  static constexpr int kMiscOff = (kBarOff + kNumBars * 8 + 15) / 16 * 16;  // what follows is read as float4
   static constexpr int kStatOff = kMiscOff + 32;       // lse / delta: [2 buffers][2][128] fp32
   static constexpr int kSmemBytes = kStatOff + 2 * 2 * kBlk * 4;  // the dynamic window must start 1024-aligned
+  static_assert(kStatOff % 16 == 0, "lse / delta are read as float4");
   static constexpr int kPieceBytes = kBlk * 128;       // dQ staging piece: [128 rows x 32 fp32]
   static constexpr uint32_t kTmemDK = 0, kTmemDV = D, kTmemS = 256, kTmemDP = 384;
 };
@@ -82,6 +79,19 @@ __device__ __forceinline__ void q_block_range(const BwdParams& p, int sq, int sk
   if (p.window_left >= 0) q_hi = min(sq, n_last - off + p.window_left + 1);
   m_start = q_lo / kBlk;
   n_m = (q_hi > q_lo) ? ((q_hi + kBlk - 1) / kBlk - m_start) : 0;
+}
+
+// Position of an iteration in the CTA's walk over (query head of the GQA group, query block), advanced
+// without integer divisions: iteration it is head g = it / n_m of the group, query block m_start + it % n_m.
+struct Walk {
+  int g, mi;
+};
+__device__ __forceinline__ Walk walk_next(Walk w, int n_m) {
+  if (++w.mi == n_m) {
+    w.mi = 0;
+    ++w.g;
+  }
+  return w;
 }
 
 __device__ __forceinline__ KvTile get_kv_tile(const BwdParams& p, int t) {
@@ -237,9 +247,11 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       // ---------------------------------------------------------------- loader
       // K, V and the first Q / dO tiles were requested during set-up.
       bool ok = true;
+      Walk w{0, 0};
       for (int it = 1; it < n_iter && ok; ++it) {
-        const int hq = ti.hk * p.group + it / ti.n_m;
-        const int m0 = (ti.m_start + it % ti.n_m) * kBlk;
+        w = walk_next(w, ti.n_m);
+        const int hq = ti.hk * p.group + w.g;
+        const int m0 = (ti.m_start + w.mi) * kBlk;
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1;
         ok = mbar_wait(&q_empty[st], ph ^ 1, ctl, kWaitBwd + 1);
@@ -293,17 +305,17 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       // is usable once the fixer warp has cleared them. bit st of *_par: parity of the stage's next fix.
       const bool packed = p.cu_q != nullptr;
       uint32_t qfix_par = 0, dofix_par = 0;
-      auto ragged_q = [&](int it) { return packed && (ti.m_start + it % ti.n_m) * kBlk + kBlk > ti.sq; };
-      auto q_ready = [&](int it, uint32_t st, uint32_t ph, int code) -> bool {
+      auto ragged_q = [&](int mi) { return packed && (ti.m_start + mi) * kBlk + kBlk > ti.sq; };
+      auto q_ready = [&](int mi, uint32_t st, uint32_t ph, int code) -> bool {
         if (!mbar_wait(&q_full[st], ph, ctl, code)) return false;
-        if (!ragged_q(it)) return true;
+        if (!ragged_q(mi)) return true;
         const uint32_t par = (qfix_par >> st) & 1;
         qfix_par ^= 1u << st;
         return mbar_wait(&q_fixed[st], par, ctl, kWaitBwd + 21);
       };
-      auto do_ready = [&](int it, uint32_t st, uint32_t ph, int code) -> bool {
+      auto do_ready = [&](int mi, uint32_t st, uint32_t ph, int code) -> bool {
         if (!mbar_wait(&do_full[st], ph, ctl, code)) return false;
-        if (!ragged_q(it)) return true;
+        if (!ragged_q(mi)) return true;
         const uint32_t par = (dofix_par >> st) & 1;
         dofix_par ^= 1u << st;
         return mbar_wait(&do_fixed[st], par, ctl, kWaitBwd + 22);
@@ -311,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       bool ok = n_iter > 0;
       if (ok) ok = mbar_wait(kv_full, 0, ctl, kWaitBwd + 3);
       if (ok && packed && ti.n0 + kBlk > ti.sk) ok = mbar_wait(kv_fixed, 0, ctl, kWaitBwd + 20);
-      if (ok) ok = q_ready(0, 0, 0, kWaitBwd + 4);
+      if (ok) ok = q_ready(0, 0, 0, kWaitBwd + 4);  // iteration 0 is query block m_start
       if (ok) {
         tc_fence_after();
         kmajor_pair(tmem + Cfg::kTmemS, k_kmaj, q_kmaj);
@@ -323,7 +335,9 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         kmajor_pair(tmem + Cfg::kTmemDP, v_kmaj, do_kmaj);
         mma_commit(dp_full);
       }
+      Walk wn{0, 0};  // position of iteration it + 1
       for (int it = 0; it < n_iter && ok; ++it) {
+        wn = walk_next(wn, ti.n_m);
         const uint32_t st = it & 1;
         const uint32_t nph = ((it + 1) >> 1) & 1;  // phase of the stage barriers of iteration it + 1
         const bool has_next = it + 1 < n_iter;
@@ -340,18 +354,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           });
         }
         mma_commit(&do_empty[st]);
-#if FA2_BWD_EARLY_S
-        // S^T of the next iteration, right behind dV: the tensor pipe executes in issue order, so dV has read
-        // P^T before these MMAs overwrite the columns, and the compute warps find the next scores ready when
-        // they finish dS^T instead of waiting for dQ and S^T after it.
-        if (has_next) {
-          ok = q_ready(it + 1, st ^ 1, nph, kWaitBwd + 8);
-          if (!ok) break;
-          tc_fence_after();
-          kmajor_pair(tmem + Cfg::kTmemS, k_kmaj, q_kmaj + (st ^ 1) * kTile16);
-          mma_commit(s_full);
-        }
-#endif
         // dQ = dS K   (into the dP^T columns, which the compute warps have drained)
         ok = mbar_wait(ds_full, it & 1, ctl, kWaitBwd + 7);
         if (!ok) break;
@@ -363,16 +365,13 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           });
           mma_commit(dq_full);
         }
-#if !FA2_BWD_EARLY_S
-        // S^T of the next iteration
         if (has_next) {
-          ok = q_ready(it + 1, st ^ 1, nph, kWaitBwd + 8);
+          ok = q_ready(wn.mi, st ^ 1, nph, kWaitBwd + 8);
           if (!ok) break;
           tc_fence_after();
           kmajor_pair(tmem + Cfg::kTmemS, k_kmaj, q_kmaj + (st ^ 1) * kTile16);
           mma_commit(s_full);
         }
-#endif
         // dK += dS^T Q
         {
           const uint64_t b = q_mn + st * kTile16;
@@ -384,7 +383,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         mma_commit(&q_empty[st]);
         // dP^T of the next iteration, once the dQ tile has left TMEM
         if (has_next) {
-          ok = do_ready(it + 1, st ^ 1, nph, kWaitBwd + 9);
+          ok = do_ready(wn.mi, st ^ 1, nph, kWaitBwd + 9);
           if (ok && want_dq) ok = mbar_wait(dq_free, it & 1, ctl, kWaitBwd + 10);
           if (!ok) break;
           tc_fence_after();
@@ -423,8 +422,9 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           publish(kv_fixed);
         }
       }
-      for (int it = 0; it < n_iter && ok; ++it) {
-        const int first = ti.sq - (ti.m_start + it % ti.n_m) * kBlk;
+      Walk w{0, 0};
+      for (int it = 0; it < n_iter && ok; ++it, w = walk_next(w, ti.n_m)) {
+        const int first = ti.sq - (ti.m_start + w.mi) * kBlk;
         const uint32_t st = it & 1, ph = (it >> 1) & 1;
         ok = __all_sync(0xffffffffu, mbar_wait(&q_full[st], ph, ctl, kWaitBwd + 4));
         if (ok && first < kBlk) {
@@ -453,9 +453,9 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     // LSE (log2 domain) and delta of one query block: thread ct < 128 loads LSE of row ct, the others
     // delta of row ct - 128; rows past the sequence give P = 0. The value for iteration it + 1 is
     // requested while iteration it computes, so its latency never sits in front of phase A.
-    auto load_stat = [&](int it) -> float {
-      const int hq = ti.hk * p.group + it / ti.n_m;
-      const int q = (ti.m_start + it % ti.n_m) * kBlk + (ct & 127);
+    auto load_stat = [&](Walk w) -> float {
+      const int hq = ti.hk * p.group + w.g;
+      const int q = (ti.m_start + w.mi) * kBlk + (ct & 127);
       if (ct < kBlk) {
         float v = INFINITY;
         if (q < ti.sq) v = p.lse[ti.bq * p.lse_batch_stride + hq * p.lse_head_stride + ti.q_row0 + q] * kLog2e;
@@ -467,12 +467,15 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       return v;
     };
     const bool fancy = (p.softcap > 0.f) || (p.alibi != nullptr);
-    float stat_next = n_iter > 0 ? load_stat(0) : 0.f;
+    Walk w{0, 0};
+    float stat_next = n_iter > 0 ? load_stat(w) : 0.f;
     for (int it = 0; it < n_iter; ++it) {
-      const int m0 = (ti.m_start + it % ti.n_m) * kBlk;
+      const int m0 = (ti.m_start + w.mi) * kBlk;
+      const int g_cur = w.g;
+      w = walk_next(w, ti.n_m);
       float* stat = s_stat + (it & 1) * (2 * kBlk);
       stat[ct] = stat_next;
-      if (it + 1 < n_iter) stat_next = load_stat(it + 1);
+      if (it + 1 < n_iter) stat_next = load_stat(w);
       mbar_arrive(stat_full);
       const bool stat_ok = mbar_wait(stat_full, it & 1, ctl, kWaitBwd + 15);  // voted on with s_full below
       const float4* lse4 = reinterpret_cast<const float4*>(stat + wg * 64);
@@ -515,7 +518,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       } else {
         // softcap / ALiBi: P follows the transformed scores of the forward; what goes on to dS is
         // P times the derivative of the transform, 1 - tanh^2 (the ALiBi bias is a constant).
-        const int hq = ti.hk * p.group + it / ti.n_m;
+        const int hq = ti.hk * p.group + g_cur;
         const float slope = (p.alibi != nullptr) ? p.alibi[ti.b * p.alibi_batch_stride + hq] * kLog2e : 0.f;
         const float inv_cap = (p.softcap > 0.f) ? p.scale / p.softcap : 0.f;
         const float cap_l2 = p.softcap * kLog2e;
@@ -582,7 +585,9 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       uint16_t* gptr = reinterpret_cast<uint16_t*>(wg == 0 ? p.dk_ptr : p.dv_ptr);
       const bool store = (p.which & 2) != 0;
       const bool tma_store = (p.cu_k == nullptr) || (ti.n0 + kBlk <= ti.sk);
-      uint8_t* stage = s_q + wg * Cfg::kTileBytes;
+      // Staging tile of the bulk store: the K tile for dK, the V tile for dV (their last readers have completed
+      // with dkv_done; the Q and dO stages may still hold dQ pieces of the last iteration's drain).
+      uint8_t* stage = (wg == 0) ? s_k : s_v;
       bool done = true;
       if (n_iter > 0) done = warp_wait(dkv_done, 0, ctl, kWaitBwd + 13);
       if (done && store) {
@@ -627,18 +632,18 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   } else {
     // ------------------------------------------------------------------ dQ drain
     // The whole 128 x D fp32 tile goes to registers at once so that the dP^T / dQ columns are free
-    // for the next iteration right away; it then leaves through the dO stage this iteration has
-    // retired as cp.reduce.async.bulk adds into the accumulator.
+    // for the next iteration right away; it then leaves through the dO stage and the Q stage this
+    // iteration has retired as cp.reduce.async.bulk adds into the accumulator.
     reg_alloc<kDrainRegs>();
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_dq = tmem + lane_addr + Cfg::kTmemDP;
     if (want_dq) {
       bool ok = true;
-      for (int it = 0; it < n_iter && ok; ++it) {
-        const int hq = ti.hk * p.group + it / ti.n_m;
-        const int m0 = (ti.m_start + it % ti.n_m) * kBlk;
+      Walk w{0, 0};
+      for (int it = 0; it < n_iter && ok; ++it, w = walk_next(w, ti.n_m)) {
+        const int hq = ti.hk * p.group + w.g;
+        const int m0 = (ti.m_start + w.mi) * kBlk;
         const uint32_t st = it & 1;
-        uint8_t* stage = s_do + st * Cfg::kTileBytes;
         if (!warp_wait(dq_full, it & 1, ctl, kWaitBwd + 14)) break;
         tc_fence_after();
         uint32_t acc[D];
@@ -654,14 +659,17 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
 #pragma unroll
           for (int i = 0; i < D; ++i) acc[i] = 0u;
         }
-        // Each warp drains its own 32 rows: pieces of 32 fp32 columns (4 KB) roll through the warp's share
-        // of the stage (two buffers at D = 128). Piece k is staged as soon as the reduce of piece k - kBufs
-        // has read its buffer, so the reduce engine always has a piece queued, and nothing but the warp
+        // Each warp drains its own 32 rows in pieces of 32 fp32 columns (4 KB). The reduce engine is bound by
+        // the latency of the L2 adds, not by bandwidth: with only the dO stage as staging (half of the tile in
+        // flight) a tile took 4000-4800 cycles and paced the whole loop. The first half of the pieces goes
+        // through the warp's share of the retired dO stage at once, the second half through its share of the
+        // Q stage as soon as dK has read it, so the whole tile is in flight together. Nothing but the warp
         // itself has to be synchronised.
         constexpr int kPieces = D / 32;
-        constexpr int kBufs = (Cfg::kTileBytes >= 2 * Cfg::kPieceBytes) ? 2 : 1;
+        constexpr int kHalf = kPieces / 2;              // pieces per staging area
         constexpr int kWarpPiece = Cfg::kPieceBytes / 4;
-        uint8_t* warp_stage = stage + (warp & 3) * (kBufs * kWarpPiece);
+        static_assert(kHalf * Cfg::kPieceBytes <= Cfg::kTileBytes, "half of the dQ tile fits one stage");
+        uint8_t* stage_do = s_do + st * Cfg::kTileBytes + (warp & 3) * (kHalf * kWarpPiece);
         int* turn = nullptr;
         if (p.dq_turn != nullptr) {
           // Ordered mode: the key blocks that add into these rows take their turns in descending order,
@@ -702,11 +710,12 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         }
 #pragma unroll
         for (int k = 0; k < kPieces; ++k) {
-          uint8_t* buf = warp_stage + (k % kBufs) * kWarpPiece;
-          if (k >= kBufs) {
-            if (lane == 0) tma_wait_group_read<kBufs - 1>();
+          // dO stage only: piece k reuses the buffer of piece k - kHalf once its reduce has read it
+          if (k >= kHalf) {
+            if (lane == 0) tma_wait_group_read<kHalf - 1>();
             __syncwarp();
           }
+          uint8_t* buf = stage_do + (k % kHalf) * kWarpPiece;
           uint8_t* rowp = buf + lane * 128;
 #pragma unroll
           for (int c = 0; c < 8; ++c)
@@ -720,7 +729,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           }
         }
         if (!ok) break;
-        // Hand the stage back to the loader once the last reduces have read it.
+        // Hand both stages back to the loader once the reduces have read them.
         if (lane == 0) {
           tma_wait_group_read<0>();
           mbar_arrive(&do_empty[st]);

@@ -2,24 +2,21 @@
 //
 // One persistent CTA per SM walks a longest-first list of work tiles. A work tile is 256 query
 // rows of one (batch, head): two 128-row "stages" that run independently of each other and share
-// the K/V tiles in shared memory. 512 threads in four warpgroups:
+// the K/V tiles in shared memory.
 //
 //   warps 0-3    stage 0 } softmax: tcgen05.ld one S row per thread (the S region of TMEM is handed back
 //   warps 4-7    stage 1 }   to the MMA warp at once, so the next Q K^T runs under this softmax) -> mask,
 //                            row max, exp2, row sum -> bf16/fp16 P written to shared memory in pieces, as the
 //                            K-major swizzled A operand of P V; O in TMEM is rescaled only when the row max
-//                            grew by more than 2^8. At the end of a tile the warps leave the row's (max, sum)
-//                            in shared memory and go straight on to the next tile.
-//   warps 8-11   epilogue : when the last P V of a stage's tile has completed: O from TMEM, O / l -> 16-bit
-//                           -> global memory (one row per thread, predicated on the row and the head dim),
-//                           LSE = (m + log2 l) ln 2; rows that see no key get O = 0 and LSE = +inf. The O
-//                           columns are handed back as soon as they are in registers.
-//   warp 12, 13  mma      : one thread per stage issues tcgen05.mma; S = Q K^T (smem x smem) into TMEM one
+//                            grew by more than 2^8. At the end of a tile the same warps run the stage's
+//                            epilogue: O / l -> 16-bit -> swizzled smem (the P buffer) -> TMA store
+//                            (predicated stores on ragged packed tiles), LSE = (m + log2 l) ln 2.
+//   warp 8, 10   mma      : one thread per stage issues tcgen05.mma; S = Q K^T (smem x smem) into TMEM one
 //                           key tile ahead, O += P V (smem x smem, V as an MN-major operand) piece by piece
-//   warp 14      loader   : TMA (cp.async.bulk.tensor, 128B swizzle) Q stages + K/V ring in the order
+//   warp 9       loader   : TMA (cp.async.bulk.tensor, 128B swizzle) Q stages + K/V ring in the order
 //                           K(0) K(1) V(0) K(2) V(1) ...; it leaves last, after every commit on its
 //                           barriers has landed
-//   warp 15      fixer    : packed batches only. The rows of a V tile that lie past the end of the sequence
+//   warp 11      fixer    : packed batches only. The rows of a V tile that lie past the end of the sequence
 //                           belong to the next sequence (P is exactly zero there, but 0 x NaN is NaN); it
 //                           clears them in shared memory once the tile has landed, before the MMA threads
 //                           may read it (the reference zero-fills them while staging,
@@ -28,9 +25,12 @@
 //
 // A stage never waits for the other one: each has its own issuing thread, barriers and counters, and a
 // K/V ring slot is released by one commit of each issuer, so stage 0 may already work on the next tile
-// while stage 1 finishes the current one. Every asynchronous arrival (TMA bytes, tcgen05.commit) has a
-// waiter before the CTA ends, and no thread of a warp that executes .sync.aligned tcgen05 instructions runs
-// lane-divergent code other than bounded polling loops that end in a warp vote.
+// while stage 1 finishes the current one. Every asynchronous arrival (TMA bytes, tcgen05.commit, bulk
+// stores) has a waiter before the CTA ends.
+//
+// A variant with a separate epilogue warpgroup (O read and stored by four more warps while the softmax
+// warps go on) was built and measured slower at S = 2048: O is single-buffered in TMEM, so the epilogue's
+// latency stays on the path to the next tile's first P V, and the softmax warps lose 24 registers to it.
 //
 // Replaces the reference kernels flash_attn_fwd / varlen_fwd
 // (flash-attn2-rs/src/device/forward/dense.rs:472-590, forward/mod.rs:1162-1407,
@@ -43,6 +43,9 @@
 #ifndef FA2_PQ
 #define FA2_PQ 4
 #endif
+#ifndef FA2_FWD_SPIN
+#define FA2_FWD_SPIN 1  // 1: the hand-offs inside a stage's epilogue spin on the barrier instead of parking
+#endif
 
 namespace fa2 {
 
@@ -50,23 +53,14 @@ namespace {
 
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
-constexpr int kThreads = 512;
-constexpr int kEpiWarp = 8;    // first warp of the epilogue warpgroup
-constexpr int kMmaWarp = 12;   // issues the MMAs of stage 0 (warp 13: stage 1); owns the TMEM allocation
-constexpr int kLoadWarp = 14;
-constexpr int kFixWarp = 15;
-// Registers per thread after the warpgroups have traded them (setmaxnreg): 2 x 128 x 184 + 128 x 64 + 128 x 80
-// = 65536, the whole register file.
-#ifndef FA2_FWD_REGS_S
-#define FA2_FWD_REGS_S 184
-#define FA2_FWD_REGS_E 64
-#define FA2_FWD_REGS_O 80
-#endif
-constexpr int kSoftmaxRegs = FA2_FWD_REGS_S;
-constexpr int kEpiRegs = FA2_FWD_REGS_E;
-constexpr int kOtherRegs = FA2_FWD_REGS_O;
-static_assert(2 * kSoftmaxRegs + kEpiRegs + kOtherRegs <= 512, "the four warpgroups share 64 K registers");
-constexpr int kPQ = FA2_PQ;                // P is handed to the MMA warp in kPQ pieces of kBlockN / kPQ keys
+constexpr int kThreads = 384;   // 8 softmax warps + one warpgroup holding the MMA and the loader warp
+constexpr int kMmaWarp = 8;   // issues the MMAs of stage 0
+constexpr int kMmaWarp1 = 10;  // issues the MMAs of stage 1
+constexpr int kLoadWarp = 9;
+constexpr int kFixWarp = 11;
+constexpr int kSoftmaxRegs = 200;
+constexpr int kOtherRegs = 104;
+constexpr int kPQ = FA2_PQ;                        // P is handed to the MMA warp in kPQ pieces of kBlockN / kPQ keys
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain
 
 template <int D>
@@ -76,14 +70,15 @@ struct FwdCfg {
   static constexpr int kSlots = (D == 128) ? 3 : 6;        // K/V ring depth
   static constexpr int kQOff = 0;
   static constexpr int kKVOff = 2 * kTileBytes;
-  // One buffer per stage that holds P (128 x 128 16-bit, the A operand of P V).
+  // One buffer per stage that holds P (128 x 128 16-bit, the A operand of P V) during the key loop and
+  // the output tile for the TMA store in the epilogue.
   static constexpr int kPBytes = kBlockM * kBlockN * 2;
-  static constexpr int kPOff = kKVOff + kSlots * kTileBytes;
-  static constexpr int kBarOff = kPOff + 2 * kPBytes;
-  static constexpr int kNumBars = 3 * kSlots + 2 * (9 + kPQ);  // kv_full, kv_empty, kv_fixed + per stage
-  static constexpr int kMiscOff = kBarOff + kNumBars * 8;  // tmem slot, abort flag
-  static constexpr int kStatOff = kMiscOff + 32;           // [2 stages][128 rows] (max, sum) fp32
-  static constexpr int kSmemBytes = kStatOff + 2 * kBlockM * 8;  // the dynamic window must start 1024-aligned
+  static constexpr int kStageBufBytes = kTileBytes > kPBytes ? kTileBytes : kPBytes;
+  static constexpr int kOOff = kKVOff + kSlots * kTileBytes;
+  static constexpr int kBarOff = kOOff + 2 * kStageBufBytes;
+  static constexpr int kNumBars = 3 * kSlots + 18 + 2 * kPQ;  // kv_full, kv_empty, kv_fixed + per stage
+  static constexpr int kMiscOff = (kBarOff + kNumBars * 8 + 15) / 16 * 16;  // tmem slot, abort flag
+  static constexpr int kSmemBytes = kMiscOff + 32;  // the dynamic window must start 1024-aligned
   static constexpr uint32_t kTmemS0 = 0, kTmemS1 = 128, kTmemO0 = 256, kTmemO1 = 256 + D;
 };
 
@@ -99,23 +94,52 @@ struct Tile {
   bool valid;
 };
 
-__device__ __forceinline__ Tile get_tile(const FwdParams& p, int t) {
+// Divisors of the work-list index, with their float reciprocals: an integer division is a long dependent
+// chain, every role walks the list, and the softmax warps do so between two tiles while the other stage's warp
+// keeps the scheduler busy. n / d for 0 <= n < 2^24 is the float estimate walked to the exact quotient.
+// The four reciprocals live in shared memory (written once by thread 0), not in registers.
+struct ListDiv {
+  float inv_grid, inv_bh, inv_heads, inv_group;
+};
+__device__ __forceinline__ void make_list_div(const FwdParams& p, volatile ListDiv* d) {
+  d->inv_grid = __frcp_rn(__int2float_rn(static_cast<int>(gridDim.x)));
+  d->inv_bh = __frcp_rn(__int2float_rn(p.batch * p.heads));
+  d->inv_heads = __frcp_rn(__int2float_rn(p.heads));
+  d->inv_group = __frcp_rn(__int2float_rn(p.group));
+}
+__device__ __forceinline__ int div_small(int n, int d, float inv) {
+  if (n >= (1 << 24)) return n / d;
+  int q = __float2int_rz(__int2float_rz(n) * inv);
+  int r = n - q * d;
+  while (r >= d) {
+    ++q;
+    r -= d;
+  }
+  while (r < 0) {
+    --q;
+    r += d;
+  }
+  return q;
+}
+
+__device__ __forceinline__ Tile get_tile(const FwdParams& p, const volatile ListDiv* ldp, int t) {
+  const ListDiv ld{ldp->inv_grid, ldp->inv_bh, ldp->inv_heads, ldp->inv_group};
   Tile ti;
   // Work tiles are listed longest first; CTA c takes list entries c, 2G-1-c, 2G+c, 4G-1-c, ... (G CTAs):
   // reversing every other round evens out the work per CTA when the sizes fall off in plateaus.
   const int grid = static_cast<int>(gridDim.x);
-  const int round = t / grid;
+  const int round = div_small(t, grid, ld.inv_grid);
   const int pos = (round & 1) ? round * grid + (grid - 1 - (t - round * grid)) : t;
   if (pos >= p.num_tiles) {
     ti.valid = false;
     return ti;
   }
   const int bh = p.batch * p.heads;
-  const int mrev = pos / bh;
+  const int mrev = div_small(pos, bh, ld.inv_bh);
   const int rem = pos - mrev * bh;
-  ti.b = rem / p.heads;
+  ti.b = div_small(rem, p.heads, ld.inv_heads);
   ti.h = rem - ti.b * p.heads;
-  ti.hk = ti.h / p.group;
+  ti.hk = div_small(ti.h, p.group, ld.inv_group);
   ti.m0 = (p.num_mblk - 1 - mrev) * (2 * kBlockM);
   if (p.cu_q != nullptr) {
     ti.q_row0 = p.cu_q[ti.b];
@@ -123,8 +147,7 @@ __device__ __forceinline__ Tile get_tile(const FwdParams& p, int t) {
     ti.k_row0 = p.cu_k[ti.b];
     ti.sk = p.cu_k[ti.b + 1] - ti.k_row0;
     ti.bq = 0;
-    // Inconsistent metadata is skipped, as the reference kernel does
-    // (flash-attn2-rs/src/device/varlen/mod.rs:112-127).
+    // Inconsistent metadata is skipped, as the reference kernel does.
     if (ti.sq < 0 || ti.sk < 0 || ti.sq > p.seqlen_q || ti.sk > p.seqlen_k || ti.q_row0 < 0 || ti.k_row0 < 0) ti.sq = 0;
   } else {
     ti.q_row0 = 0;
@@ -165,9 +188,9 @@ __device__ __forceinline__ Tile get_tile(const FwdParams& p, int t) {
 
 // First row of key tile j that lies past the end of a packed sequence (kBlockN = none). Dense tensors need
 // nothing: the TMA unit fills rows past the tensor with zeros.
-__device__ __forceinline__ int ragged_row(const FwdParams& p, const Tile& ti, int j) {
+__device__ __forceinline__ int ragged_row(const FwdParams& p, int sk, int j) {
   if (p.cu_q == nullptr) return kBlockN;
-  const int left = ti.sk - j * kBlockN;
+  const int left = sk - j * kBlockN;
   return left < kBlockN ? max(left, 0) : kBlockN;
 }
 
@@ -188,34 +211,32 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   }
   uint8_t* s_q = smem + Cfg::kQOff;
   uint8_t* s_kv = smem + Cfg::kKVOff;
-  uint8_t* s_p = smem + Cfg::kPOff;
+  uint8_t* s_o = smem + Cfg::kOOff;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOff);
-  uint64_t* kv_full = bars;                    // TMA bytes of the slot's tile have landed
-  uint64_t* kv_empty = bars + Cfg::kSlots;     // both issuers' MMAs on the slot have completed
-  uint64_t* kv_fixed = bars + 2 * Cfg::kSlots; // the fixer has cleared the stray rows of a ragged V tile
-  uint64_t* st_bars = bars + 3 * Cfg::kSlots;  // every array below is [2], one per stage
-  uint64_t* q_full = st_bars;
-  uint64_t* q_empty = st_bars + 2;
-  uint64_t* s_full = st_bars + 4;
-  uint64_t* s_free = st_bars + 6;       // S_s has been read out of TMEM: the next Q K^T may overwrite it
-  uint64_t* pv_done = st_bars + 8;      // P V(j) of stage s has completed: P_s may be overwritten, O_s rescaled
-  uint64_t* o_full = st_bars + 10;      // the last P V of the stage's tile has completed
-  uint64_t* o_free = st_bars + 12;      // O_s has been read out of TMEM by the epilogue
-  uint64_t* stat_full = st_bars + 14;   // the softmax warps have left (max, sum) of the tile's rows
-  uint64_t* stat_free = st_bars + 16;   // the epilogue has read them
-  uint64_t* p_full = st_bars + 18;      // [2][kPQ]: piece q of P_s is in shared memory
+  uint64_t* kv_full = bars;
+  uint64_t* kv_empty = bars + Cfg::kSlots;
+  uint64_t* kv_fixed = bars + 2 * Cfg::kSlots;  // the fixer has cleared the stray rows of a ragged V tile
+  uint64_t* q_full = bars + 3 * Cfg::kSlots;    // every array below is [2], one per stage
+  uint64_t* q_empty = q_full + 2;
+  uint64_t* s_full = q_full + 4;
+  uint64_t* s_free = q_full + 16;        // S_s has been read out of TMEM: the next Q K^T may overwrite it
+  uint64_t* p_full = q_full + 18;        // [2][kPQ]: piece q of P_s is in shared memory
+  uint64_t* pv_done = q_full + 8;
+  uint64_t* o_free = q_full + 10;        // O_s has been read out of TMEM
+  uint64_t* epi_full = q_full + 12;      // all 128 rows of O_s are staged in smem
+  uint64_t* o_stage_free = q_full + 14;  // the previous TMA store of stage s has read its staging tile
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::kMiscOff + 8);
-  float2* s_stat = reinterpret_cast<float2*>(smem + Cfg::kStatOff);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const WaitCtl ctl{abort_flag, p.status};
-  const bool packed = p.cu_q != nullptr;
+  volatile ListDiv* ld = reinterpret_cast<volatile ListDiv*>(smem + Cfg::kMiscOff + 16);
 
   if (tid == 0) {
     *abort_flag = 0;
+    make_list_div(p, ld);
     for (int i = 0; i < Cfg::kSlots; ++i) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 2);  // one commit per issuer
@@ -225,13 +246,12 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
       mbar_init(&q_full[s], 1);
       mbar_init(&q_empty[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_free[s], kBlockM);
-      mbar_init(&pv_done[s], 1);
-      mbar_init(&o_full[s], 1);
-      mbar_init(&o_free[s], kBlockM);
-      mbar_init(&stat_full[s], kBlockM);
-      mbar_init(&stat_free[s], kBlockM);
       for (int q = 0; q < kPQ; ++q) mbar_init(&p_full[s * kPQ + q], kBlockM);
+      mbar_init(&pv_done[s], 1);
+      mbar_init(&o_free[s], kBlockM);
+      mbar_init(&s_free[s], kBlockM);
+      mbar_init(&epi_full[s], kBlockM);
+      mbar_init(&o_stage_free[s], 1);
     }
     mbar_fence_init();
   }
@@ -243,6 +263,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
     tma_prefetch_desc(&p.tm_q);
     tma_prefetch_desc(&p.tm_k);
     tma_prefetch_desc(&p.tm_v);
+    tma_prefetch_desc(&p.tm_o);
   }
   tc_fence_before();
   __syncthreads();
@@ -250,35 +271,35 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   const uint32_t tmem = *tmem_slot;
 
   if (warp < 8) {
-    // ------------------------------------------------------------------ softmax of stage s
+    // ------------------------------------------------------------------ softmax + epilogue of stage s
     reg_alloc<kSoftmaxRegs>();
     const int s = warp >> 2;
     const int row_in = tid & 127;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_s = tmem + lane_addr + (s == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1);
     const uint32_t t_o = tmem + lane_addr + (s == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
+    uint8_t* stage_smem = s_o + s * Cfg::kStageBufBytes;
     // P of this stage as the K-major, 128-byte swizzled A operand of P V: key chunk c (8 keys, 16 bytes) of
     // row r sits in atom c / 8 at byte 128 r + 16 ((c % 8) ^ (r % 8)).
-    const uint32_t p_row = smem_u32(s_p + s * Cfg::kPBytes) + row_in * 128;
+    const uint32_t p_row = smem_u32(stage_smem) + row_in * 128;
     const uint32_t p_swz = static_cast<uint32_t>(row_in & 7) << 4;
     auto store_p_chunk = [&](const int c, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
       const uint32_t addr = p_row + (c >> 3) * (kBlockM * 128) + ((static_cast<uint32_t>(c & 7) << 4) ^ p_swz);
       asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
     };
     const bool fancy = (p.softcap > 0.f) || (p.alibi != nullptr) || (p.scale_log2 < 0.f);
-    uint32_t n_sfull = 0, n_pv = 0, n_tile = 0;
-    bool ok = true;
-    for (int t = blockIdx.x; t - static_cast<int>(blockIdx.x) < p.num_tiles && ok; t += gridDim.x) {
-      const Tile ti = get_tile(p, t);
+    uint32_t n_sfull = 0, n_pv = 0, n_store = 0, n_first = 0;
+    for (int t = blockIdx.x; t - static_cast<int>(blockIdx.x) < p.num_tiles; t += gridDim.x) {
+      const Tile ti = get_tile(p, ld, t);
       if (!ti.valid) continue;
-      const int nb_s = s ? ti.nb[1] : ti.nb[0];
-      const int ne_s = s ? ti.ne[1] : ti.ne[0];
-      if (ne_s <= nb_s) continue;  // no key is visible to this stage: the epilogue writes O = 0, LSE = +inf
       const int r_lo = ti.m0 + s * kBlockM;
       const int row = r_lo + row_in;
+      const int nb_s = s ? ti.nb[1] : ti.nb[0];
+      const int ne_s = s ? ti.ne[1] : ti.ne[0];
       float m = -INFINITY, l = 0.f;
       float slope = 0.f;
       if (p.alibi != nullptr) slope = p.alibi[ti.b * p.alibi_batch_stride + ti.h] * 1.4426950408889634f;
+      bool ok = true;
       for (int j = nb_s; j < ne_s; ++j) {
         if (!warp_wait(&s_full[s], n_sfull & 1, ctl, kWaitSoftmaxSFull)) { ok = false; break; }
         ++n_sfull;
@@ -334,21 +355,23 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             l *= alpha;
           }
         } else {
-          // Scores leave this block already in the log2 domain.
-          const float inv_cap = (p.softcap > 0.f) ? p.scale / p.softcap : 0.f;
-          const float cap_l2 = p.softcap * 1.4426950408889634f;
-#pragma unroll
-          for (int i = 0; i < kBlockN; ++i) {
-            float x = __uint_as_float(sr[i]);
-            x = (p.softcap > 0.f) ? cap_l2 * tanh_approx(x * inv_cap) : x * p.scale_log2;
-            if (p.alibi != nullptr) {
-              const int col = col0 + i;
-              x += p.causal_alibi ? slope * static_cast<float>(col)
-                                  : -slope * fabsf(static_cast<float>(row + ti.off - col));
+          if (fancy) {
+            // Scores leave this block already in the log2 domain.
+            const float inv_cap = (p.softcap > 0.f) ? p.scale / p.softcap : 0.f;
+            const float cap_l2 = p.softcap * 1.4426950408889634f;
+  #pragma unroll
+            for (int i = 0; i < kBlockN; ++i) {
+              float x = __uint_as_float(sr[i]);
+              x = (p.softcap > 0.f) ? cap_l2 * tanh_approx(x * inv_cap) : x * p.scale_log2;
+              if (p.alibi != nullptr) {
+                const int col = col0 + i;
+                x += p.causal_alibi ? slope * static_cast<float>(col)
+                                    : -slope * fabsf(static_cast<float>(row + ti.off - col));
+              }
+              sr[i] = __float_as_uint(x);
             }
-            sr[i] = __float_as_uint(x);
+            cs = 1.f;
           }
-          cs = 1.f;
           if (need_mask) {
             int hi = ti.sk;
             if (p.window_right >= 0) hi = min(hi, row + ti.off + p.window_right + 1);
@@ -356,20 +379,21 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             if (p.window_left >= 0) lo = row + ti.off - p.window_left;
             hi -= col0;
             lo -= col0;
-#pragma unroll
+  #pragma unroll
             for (int i = 0; i < kBlockN; ++i)
               if (i < lo || i >= hi) sr[i] = __float_as_uint(-INFINITY);
           }
           float mx0 = __uint_as_float(sr[0]), mx1 = __uint_as_float(sr[1]);
           float mx2 = __uint_as_float(sr[2]), mx3 = __uint_as_float(sr[3]);
-#pragma unroll
+  #pragma unroll
           for (int i = 4; i < kBlockN; i += 4) {
             mx0 = fmaxf(mx0, __uint_as_float(sr[i]));
             mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
             mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2]));
             mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
           }
-          const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+          const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * cs;
+          const float m_new = fmaxf(m, m_tile);
           // Keep the stale max unless it grew by more than 2^8: the final O / l is exact either way.
           grow = (m_new - m) > kRescaleThreshold;
           if (grow) {
@@ -378,10 +402,22 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             l *= alpha;
           }
         }
-        // P V of the previous key tile (of this or of the previous work tile) has to be complete: it reads
-        // the P buffer that this iteration overwrites, and it is the only operation that touches O.
-        bool waited = true;
-        if (n_pv > 0) waited = mbar_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitSoftmaxPvDone);
+        bool waited;
+        if (j > nb_s) {
+          // P V(j-1) has to be complete: it reads the P buffer that this iteration overwrites, and it is the
+          // only operation that touches O of this stage.
+          waited = mbar_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitSoftmaxPvDone);
+        } else {
+          // First iteration of a tile: the TMA store of the previous tile must have read the buffer.
+          if (row_in == 0) {
+            tma_wait_group_read<0>();
+            mbar_arrive(&o_stage_free[s]);
+          }
+          __syncwarp();
+          waited = FA2_FWD_SPIN ? mbar_wait_spin(&o_stage_free[s], n_first & 1, ctl, kWaitEpiFinal)
+                                : mbar_wait(&o_stage_free[s], n_first & 1, ctl, kWaitEpiFinal);
+          ++n_first;
+        }
         // One warp reduction reconverges the lanes after the wait and carries both warp-uniform
         // decisions: bit 1 = a lane's wait ran out, bit 0 = a lane's row maximum grew.
         const unsigned votes = __reduce_or_sync(0xffffffffu, (grow ? 1u : 0u) | (waited ? 0u : 2u));
@@ -439,7 +475,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         } else {
           const float neg_m = (m == -INFINITY) ? 0.f : -m;
           float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-#pragma unroll
+  #pragma unroll
           for (int i = 0; i < kBlockN; i += 4) {
             const float p0 = ex2(fmaf(__uint_as_float(sr[i]), cs, neg_m));
             const float p1 = ex2(fmaf(__uint_as_float(sr[i + 1]), cs, neg_m));
@@ -453,6 +489,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             sr[i / 2 + 1] = pack2<BF16>(p2, p3);
           }
           l += (l0 + l1) + (l2 + l3);
+        }
+        if (fancy) {
 #pragma unroll
           for (int c = 0; c < kBlockN / 8; ++c) store_p_chunk(c, sr[4 * c], sr[4 * c + 1], sr[4 * c + 2], sr[4 * c + 3]);
           fence_proxy_async_smem();
@@ -462,71 +500,80 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         ++n_pv;
       }
       if (!ok) break;
-      // ---- end of the tile: hand (max, sum) of this row to the epilogue warps and go on.
-      if (!mbar_wait(&stat_free[s], (n_tile & 1) ^ 1, ctl, kWaitEpiFinal)) { ok = false; break; }
-      s_stat[s * kBlockM + row_in] = make_float2(m, l);
-      mbar_arrive(&stat_full[s]);
-      ++n_tile;
-    }
-    // The last P V of this stage: every commit on pv_done has landed before the CTA ends.
-    if (ok && n_pv > 0) mbar_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitSoftmaxPvDone);
-  } else if (warp < kMmaWarp) {
-    // ------------------------------------------------------------------ epilogue of both stages
-    reg_dealloc<kEpiRegs>();
-    const int row_in = tid - kEpiWarp * 32;
-    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    uint32_t n_epi[2] = {0, 0};
-    bool ok = true;
-    for (int t = blockIdx.x; t - static_cast<int>(blockIdx.x) < p.num_tiles && ok; t += gridDim.x) {
-      const Tile ti = get_tile(p, t);
-      if (!ti.valid) continue;
+      // ---- epilogue of this stage: O / l -> 16-bit -> swizzled smem -> one TMA store.
+      // A ragged tile of a packed batch (rows of the next sequence follow) uses predicated stores.
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o_ptr) + ti.bq * p.o_batch_stride +
+                       static_cast<int64_t>(ti.q_row0 + row) * p.o_row_stride + ti.h * p.o_head_stride;
+      const bool tma_store = (p.cu_q == nullptr) || (r_lo + kBlockM <= ti.sq);
+      if (ne_s > nb_s) {
+        const float inv_l = (l > 0.f) ? 1.f / l : 0.f;  // before the wait: the reciprocal queues behind the other stage's exp2 stream
+        if (!warp_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitEpiPvDone)) break;
+        tc_fence_after();
+        uint32_t orr[D];
 #pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        const int row = ti.m0 + s * kBlockM + row_in;
-        const bool live = row < ti.sq;
-        uint16_t* orow = reinterpret_cast<uint16_t*>(p.o_ptr) + ti.bq * p.o_batch_stride +
-                         static_cast<int64_t>(ti.q_row0 + row) * p.o_row_stride + ti.h * p.o_head_stride;
-        float* lse_row = p.lse_ptr + ti.bq * p.lse_batch_stride + ti.h * p.lse_head_stride + ti.q_row0 + row;
-        if (ti.ne[s] > ti.nb[s]) {
-          const uint32_t par = n_epi[s] & 1;
-          const bool got = mbar_wait(&stat_full[s], par, ctl, kWaitEpiFinal) && mbar_wait(&o_full[s], par, ctl, kWaitEpiPvDone);
-          if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-          ++n_epi[s];
-          const float2 ml = s_stat[s * kBlockM + row_in];
-          mbar_arrive(&stat_free[s]);
-          const float inv_l = (ml.y > 0.f) ? 1.f / ml.y : 0.f;
-          const uint32_t t_o = tmem + lane_addr + (s == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
-          tc_fence_after();
+        for (int c = 0; c < D / 32; ++c) tmem_ld32(t_o + c * 32, orr + c * 32);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&o_free[s]);
+        // The other stage's softmax warp shares this scheduler and rarely stalls, so every instruction here
+        // is dear: packed multiplies, one conversion per pair, st.shared with a precomputed row address.
+        const uint64_t il2 = pack_f32x2(inv_l, inv_l);
+        const uint32_t o_row = smem_u32(stage_smem) + row_in * 128;
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t orr[32];
-            tmem_ld32(t_o + c * 32, orr);
-            tmem_wait_ld();
-            if (c == D / 32 - 1) {
-              tc_fence_before();
-              mbar_arrive(&o_free[s]);  // the first P V of the stage's next tile may overwrite O
-            }
+        for (int c = 0; c < D / 8; ++c) {  // 16-byte chunks of the row
+          uint32_t w[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {  // 16-byte chunks of the row
-              uint4 w;
-              w.x = pack2<BF16>(__uint_as_float(orr[8 * q]) * inv_l, __uint_as_float(orr[8 * q + 1]) * inv_l);
-              w.y = pack2<BF16>(__uint_as_float(orr[8 * q + 2]) * inv_l, __uint_as_float(orr[8 * q + 3]) * inv_l);
-              w.z = pack2<BF16>(__uint_as_float(orr[8 * q + 4]) * inv_l, __uint_as_float(orr[8 * q + 5]) * inv_l);
-              w.w = pack2<BF16>(__uint_as_float(orr[8 * q + 6]) * inv_l, __uint_as_float(orr[8 * q + 7]) * inv_l);
-              if (live && c * 32 + q * 8 < p.head_dim) *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = w;
-            }
+          for (int q = 0; q < 4; ++q) {
+            float a, b;
+            unpack_f32x2(mul2(pack_f32x2(__uint_as_float(orr[8 * c + 2 * q]), __uint_as_float(orr[8 * c + 2 * q + 1])), il2), a, b);
+            w[q] = pack2<BF16>(a, b);
           }
-          if (live) *lse_row = (ml.y > 0.f) ? (ml.x + lg2(ml.y)) * 0.6931471805599453f : INFINITY;
-        } else if (live) {
-          // No key is visible to this stage's rows: O = 0, LSE = +inf.
+          if (tma_store) {
+            // chunk c lives in swizzle atom c / 8, at position (c % 8) ^ (row % 8) of the row's 128-byte line
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(o_row + (c / 8) * (kBlockM * 128) +
+                                                                             (((c & 7) ^ (row_in & 7)) << 4)),
+                         "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                         : "memory");
+          } else if (row < ti.sq && c * 8 < p.head_dim) {
+            *reinterpret_cast<uint4*>(orow + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+        if (tma_store) {
+          fence_proxy_async_smem();
+          mbar_arrive(&epi_full[s]);
+          // A wait that runs out here sets the abort flag; the warp then leaves together at its next
+          // warp_wait, which is also where the lanes meet again after this single-lane section.
+          if (row_in == 0 && (FA2_FWD_SPIN ? mbar_wait_spin(&epi_full[s], n_store & 1, ctl, kWaitEpiFinal)
+                                           : mbar_wait(&epi_full[s], n_store & 1, ctl, kWaitEpiFinal))) {
+#pragma unroll
+            for (int a = 0; a < Cfg::kAtoms; ++a)
+              if (a * 64 < p.head_dim)
+                tma_store_4d(&p.tm_o, stage_smem + a * (kBlockM * 128), a * 64, ti.h, ti.q_row0 + r_lo, ti.bq);
+            tma_commit_group();
+          }
+          __syncwarp();
+          ++n_store;
+        }
+      } else {
+        mbar_arrive(&o_free[s]);
+        if (row < ti.sq) {
+          // No key is visible to this stage: O = 0.
 #pragma unroll
           for (int q = 0; q < D / 8; ++q)
             if (q * 8 < p.head_dim) *reinterpret_cast<uint4*>(orow + q * 8) = make_uint4(0, 0, 0, 0);
-          *lse_row = INFINITY;
         }
-        __syncwarp();
       }
+      if (row < ti.sq) {
+        const float lse = (l > 0.f) ? (m + lg2(l)) * 0.6931471805599453f : INFINITY;
+        p.lse_ptr[ti.bq * p.lse_batch_stride + ti.h * p.lse_head_stride + ti.q_row0 + row] = lse;
+      }
+      // Rows past the end of a packed sequence skipped the stores above.
+      __syncwarp();
     }
+    // The last bulk store has read its staging tile, and the last P V of this stage has completed: nothing of
+    // this stage is still on its way when the CTA ends.
+    if (row_in == 0) tma_wait_group_read<0>();
+    __syncwarp();
   } else {
     reg_dealloc<kOtherRegs>();
     if (warp == kLoadWarp && lane == 0) {
@@ -547,7 +594,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         return true;
       };
       for (int t = blockIdx.x; t - static_cast<int>(blockIdx.x) < p.num_tiles && ok; t += gridDim.x) {
-        const Tile ti = get_tile(p, t);
+        const Tile ti = get_tile(p, ld, t);
         if (!ti.valid) continue;
         auto load_q = [&](int s) -> bool {
           if (ti.ne[s] <= ti.nb[s]) return true;
@@ -586,7 +633,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
       // ---------------------------------------------------------------- fixer (packed batches)
       // Walks the ring in the loader's order and waits for every tile, which keeps it within one ring
       // pass of the consumers; it acts on V tiles that reach past the end of their sequence.
-      if (packed) {
+      if (p.cu_q != nullptr) {
         uint32_t slot = 0, ring_phase = 0;
         bool ok = true;
         auto step = [&](int first_stray) -> bool {
@@ -610,16 +657,16 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           return true;
         };
         for (int t = blockIdx.x; t - static_cast<int>(blockIdx.x) < p.num_tiles && ok; t += gridDim.x) {
-          const Tile ti = get_tile(p, t);
+          const Tile ti = get_tile(p, ld, t);
           if (!ti.valid) continue;
           if (ti.jlo < ti.jhi) ok = step(kBlockN);
           for (int j = ti.jlo; j < ti.jhi && ok; ++j) {
             if (j + 1 < ti.jhi) ok = step(kBlockN);
-            if (ok) ok = step(ragged_row(p, ti, j));
+            if (ok) ok = step(ragged_row(p, ti.sk, j));
           }
         }
       }
-    } else if ((warp == kMmaWarp || warp == kMmaWarp + 1) && lane == 0) {
+    } else if ((warp == kMmaWarp || warp == kMmaWarp1) && lane == 0) {
       // ---------------------------------------------------------------- mma issuer
       // Descriptors are built once; inside the loops an operand address is one 64-bit add of a
       // compile-time constant (descriptor address field is in 16-byte units), so that the single
@@ -633,15 +680,17 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
       const uint64_t k_desc = make_smem_desc(smem_u32(s_kv), 16, 1024);                // K-major B
       const uint64_t v_desc = make_smem_desc(smem_u32(s_kv), kBlockN * 128, 1024);     // MN-major B
       // Each stage has its own issuing warp, and both walk the same sequence of tiles and K/V ring
-      // positions. A K/V slot is released by two commits, one per issuer.
-      const int s = warp - kMmaWarp;
+      // positions. A stage never waits for the other one: stage 0 may already run the next tile while
+      // stage 1 finishes the current one, and a piece of P V is issued while the other stage's
+      // exponentials are still in flight. A K/V slot is released by two commits, one per issuer.
+      const int s = (warp == kMmaWarp) ? 0 : 1;
       const uint64_t a_q = q_desc + s * kTile16;
       const uint32_t t_s = tmem + (s == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1);
       const uint32_t t_o = tmem + (s == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
-      const uint64_t a_p = make_smem_desc(smem_u32(s_p + s * Cfg::kPBytes), 16, 1024);  // P: K-major A
+      const uint64_t a_p = make_smem_desc(smem_u32(s_o + s * Cfg::kStageBufBytes), 16, 1024);  // P: K-major A
       uint32_t slot = 0, ring_phase = 0;  // K/V ring position of the next tile to consume
       uint32_t fix_par = 0;               // bit i: parity of the next kv_fixed phase of slot i
-      uint32_t n_qk = 0, n_p = 0, n_q = 0, n_work = 0;
+      uint32_t n_qk = 0, n_p = 0, n_q = 0, n_tile = 0;
       bool ok = true;
       auto advance = [&]() {
         mma_commit(&kv_empty[slot]);
@@ -651,7 +700,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         }
       };
       for (int t = blockIdx.x; t - static_cast<int>(blockIdx.x) < p.num_tiles && ok; t += gridDim.x) {
-        const Tile ti = get_tile(p, t);
+        const Tile ti = get_tile(p, ld, t);
         if (!ti.valid) continue;
         const int nb = s ? ti.nb[1] : ti.nb[0], ne = s ? ti.ne[1] : ti.ne[0];
         bool q_ready = false;
@@ -685,7 +734,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         // P row inside its swizzle atom, 16 rows of 128 bytes of V).
         auto do_v = [&](const int j) -> bool {
           if (!mbar_wait(&kv_full[slot], ring_phase, ctl, kWaitMmaKVFull)) return false;
-          if (ragged_row(p, ti, j) < kBlockN) {
+          if (ragged_row(p, ti.sk, j) < kBlockN) {
             // A V tile that reaches past its sequence is usable once the fixer has cleared the stray rows.
             if (!mbar_wait(&kv_fixed[slot], (fix_par >> slot) & 1, ctl, kWaitMmaKVFull)) return false;
             fix_par ^= 1u << slot;
@@ -697,7 +746,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
 #pragma unroll
             for (int q = 0; q < kPQ; ++q) {
               if (!mbar_wait(&p_full[s * kPQ + q], n_p & 1, ctl, kWaitMmaPFull)) return false;
-              if (q == 0 && first && !mbar_wait(&o_free[s], (n_work & 1) ^ 1, ctl, kWaitMmaOFree)) return false;
+              if (q == 0 && first && !mbar_wait(&o_free[s], (n_tile & 1) ^ 1, ctl, kWaitMmaOFree)) return false;
               tc_fence_after();
 #pragma unroll
               for (int ks = q * kStepsPerPiece; ks < (q + 1) * kStepsPerPiece; ++ks) {
@@ -708,7 +757,6 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             }
             ++n_p;
             mma_commit(&pv_done[s]);
-            if (j == ne - 1) mma_commit(&o_full[s]);  // the epilogue may read O_s
           }
           advance();
           return true;
@@ -718,7 +766,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           if (j + 1 < ti.jhi) ok = do_k(j + 1);
           if (ok) ok = do_v(j);
         }
-        if (ne > nb) ++n_work;
+        ++n_tile;
       }
     }
   }
@@ -757,7 +805,7 @@ cudaError_t launch_one(const FwdParams& p, int num_sms, cudaStream_t stream) {
 
 cudaError_t launch_fwd(const FwdParams& p, int head_dim, bool bf16, int num_sms, cudaStream_t stream) {
   if (p.num_tiles <= 0) return cudaSuccess;
-  // Head dims below the kernel's D ride on TMA: loads past the real head dim read zeros; the epilogue's stores stop there.
+  // Head dims below the kernel's D ride on TMA: loads past the real head dim read zeros, stores are clipped.
   if (head_dim > 64 && head_dim <= 128) return bf16 ? launch_one<128, true>(p, num_sms, stream) : launch_one<128, false>(p, num_sms, stream);
   if (head_dim > 0 && head_dim <= 64) return bf16 ? launch_one<64, true>(p, num_sms, stream) : launch_one<64, false>(p, num_sms, stream);
   return cudaErrorInvalidValue;

@@ -32,18 +32,28 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// One try_wait. The last operand is the suspend-time hint in nanoseconds: the hardware may park the
-// thread until the phase completes (it is woken then) or the hint expires, so a polling warp does
-// not take issue slots from the warps that share its scheduler.
+// One try_wait: the hardware may park the thread until the phase completes (it is woken then) or a
+// system-dependent time limit expires, so a polling warp does not take issue slots from the warps that share
+// its scheduler.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
+#ifdef FA2_TRYWAIT_HINT_NS
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity), "r"(0x989680u)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(FA2_TRYWAIT_HINT_NS)
       : "memory");
+#else
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+#endif
   return ok != 0;
 }
 
@@ -52,19 +62,6 @@ struct WaitCtl {
   volatile int* abort_flag;   // shared memory
   int* error_word;            // global memory, may be null
 };
-
-// Non-blocking probe of a phase, for a thread that polls several barriers in turn.
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
 
 // Upper bound of one wait in SM clock cycles (about a second at B200 clocks).
 #ifndef FA2_WAIT_LIMIT_CYCLES
@@ -79,6 +76,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     if (mbar_try_wait(bar, parity)) return true;
     if (*ctl.abort_flag) return false;
     if ((it & 7u) == 0u && clock64() - t0 > FA2_WAIT_LIMIT_CYCLES) break;
+  }
+  if (!*ctl.abort_flag) {
+    *ctl.abort_flag = 1;
+    if (ctl.error_word) atomicCAS(ctl.error_word, 0, code);
+  }
+  return false;
+}
+
+// The same wait for short hand-offs between the warps of one role: it probes the phase without letting the
+// hardware park the thread (a parked thread was seen to come back thousands of cycles after the phase
+// completed), at the price of issue slots while it spins.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, int code) {
+  const long long t0 = clock64();
+  for (uint32_t it = 1;; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (*ctl.abort_flag) return false;
+    if ((it & 15u) == 0u && clock64() - t0 > FA2_WAIT_LIMIT_CYCLES) break;
   }
   if (!*ctl.abort_flag) {
     *ctl.abort_flag = 1;
@@ -105,10 +127,6 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -180,21 +198,6 @@ __host__ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint
   return d;
 }
 
-// 32-bit instruction descriptor for kind::f16 with fp32 accumulation.
-//   [4,6) D format 1=f32; [7,10) A format; [10,13) B format (0=f16, 1=bf16);
-//   bit 15 A MN-major; bit 16 B MN-major; [17,23) N>>3; [24,29) M>>4.
-__host__ __device__ __forceinline__ uint32_t make_idesc(bool bf16, int m, int n, bool a_mn_major, bool b_mn_major) {
-  uint32_t d = 0;
-  d |= 1u << 4;
-  d |= (bf16 ? 1u : 0u) << 7;
-  d |= (bf16 ? 1u : 0u) << 10;
-  d |= (a_mn_major ? 1u : 0u) << 15;
-  d |= (b_mn_major ? 1u : 0u) << 16;
-  d |= static_cast<uint32_t>(n >> 3) << 17;
-  d |= static_cast<uint32_t>(m >> 4) << 24;
-  return d;
-}
-
 // ---------------------------------------------------------------- MMA
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -203,15 +206,6 @@ __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // Variants that add compile-time offsets (in 16-byte units) to the descriptors inside the asm
@@ -332,47 +326,20 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
   return d;
 }
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   uint64_t d;
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-// a + b rounded toward -infinity (used to take floor() with a magic constant)
-__device__ __forceinline__ uint64_t add2_rm(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.rm.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
-}
-
-// 2^x for two lanes on the FMA pipe instead of the MUFU unit: x = floor(x) + f, 2^f by a degree-3
-// minimax polynomial on [0, 1) (max relative error 8.8e-5, below the 16-bit rounding of P), the
-// integer part added into the exponent field. Inputs are clamped to >= -126.
-__device__ __forceinline__ void exp2_poly2(float& x0, float& x1) {
-  const float kMagic = 12582912.f;  // 1.5 * 2^23: fp32 spacing is 1 there
-  const uint64_t magic = pack_f32x2(kMagic, kMagic);
-  const uint64_t x = pack_f32x2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
-  const uint64_t t = add2_rm(x, magic);   // low mantissa bits hold floor(x)
-  const uint64_t fl = sub2(t, magic);     // floor(x) as fp32
-  const uint64_t fr = sub2(x, fl);        // in [0, 1)
-  uint64_t pz = fma2(fr, pack_f32x2(0.077119089663028717041015625f, 0.077119089663028717041015625f),
-                     pack_f32x2(0.227564394474029541015625f, 0.227564394474029541015625f));
-  pz = fma2(pz, fr, pack_f32x2(0.695146143436431884765625f, 0.695146143436431884765625f));
-  pz = fma2(pz, fr, pack_f32x2(1.f, 1.f));
-  float p0, p1, t0, t1;
-  unpack_f32x2(pz, p0, p1);
-  unpack_f32x2(t, t0, t1);
-  x0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
-  x1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
 }
 
 // Pack two fp32 into one 32-bit word of two 16-bit floats: `lo` in bits [0,16).
