@@ -146,6 +146,14 @@ FA2_API int fa2_layout_is_addressable(const void* ptr, const int64_t* outer_stri
 FA2_API int fa2_pack_16bit(const void* src, void* dst, const int64_t shape[4], const int64_t outer_strides[3],
                            void* stream);
 
+/* Copy of a 16-bit tensor [n0, n1, n2, d] (unit last stride) between two layouts given by their outer element
+ * strides: the general form of fa2_pack_16bit. The operator layer uses it to copy a result that was computed
+ * into a temporary back into a supplied `out` the kernels cannot write in place (not addressable, or
+ * overlapping an input), as the reference does (flash-attn2-rs/src/host/forward/mod.rs:367-375, 832-840,
+ * src/host/layout.rs:458-512). */
+FA2_API int fa2_copy_16bit(const void* src, const int64_t src_strides[3], void* dst, const int64_t dst_strides[3],
+                           const int64_t shape[4], void* stream);
+
 /* Backward that allocates nothing. No counterpart in the reference crate (its host layer always
  * allocates its workspaces through the tvm-ffi environment allocator).
  *

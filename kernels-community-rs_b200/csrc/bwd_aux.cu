@@ -131,30 +131,50 @@ cudaError_t launch_bwd_preprocess(const PreprocessParams& p, cudaStream_t stream
   return cudaGetLastError();
 }
 
-// 16-bit tensor [n0, n1, n2, d] with unit last stride and arbitrary outer strides -> contiguous copy.
-// Stands in for the reference's packing kernel (flash-attn2-rs/src/device/layout.rs:4-35), which runs
-// when a view cannot be addressed by the main kernels (there: 16-byte alignment of the row starts).
-__global__ void __launch_bounds__(256) pack_rows_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst,
-                                                        int64_t total, int n1, int n2, int d, int64_t s0, int64_t s1,
-                                                        int64_t s2) {
-  const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+// Copy of a 16-bit tensor [n0, n1, n2, d] with unit last stride between two layouts with arbitrary outer
+// strides. Stands in for the reference's packing kernel (flash-attn2-rs/src/device/layout.rs:4-35), which
+// runs when a view cannot be addressed by the main kernels (there: 16-byte alignment of the row starts), and
+// for its copy-out of a result computed into a temporary (src/host/layout.rs:458-512). VEC = 8 moves 16 bytes
+// per thread and needs both layouts to keep every row start 16-byte aligned; VEC = 1 is the general case.
+template <int VEC>
+__global__ void __launch_bounds__(256) copy_rows_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst,
+                                                        int64_t total, int n1, int n2, int dv, int64_t a0, int64_t a1,
+                                                        int64_t a2, int64_t b0, int64_t b1, int64_t b2) {
+  const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;  // one group of VEC elements
   if (i >= total) return;
-  const int c = static_cast<int>(i % d);
-  int64_t r = i / d;
+  const int c = static_cast<int>(i % dv) * VEC;
+  int64_t r = i / dv;
   const int i2 = static_cast<int>(r % n2);
   r /= n2;
   const int i1 = static_cast<int>(r % n1);
   const int64_t i0 = r / n1;
-  dst[i] = src[i0 * s0 + i1 * s1 + i2 * s2 + c];
+  const uint16_t* s = src + i0 * a0 + i1 * a1 + i2 * a2 + c;
+  uint16_t* d = dst + i0 * b0 + i1 * b1 + i2 * b2 + c;
+  if constexpr (VEC == 8) {
+    *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(s);
+  } else {
+    *d = *s;
+  }
 }
 
-cudaError_t launch_pack_rows(const void* src, void* dst, int64_t n0, int64_t n1, int64_t n2, int64_t d, int64_t s0,
-                             int64_t s1, int64_t s2, cudaStream_t stream) {
-  const int64_t total = n0 * n1 * n2 * d;
-  if (total == 0) return cudaSuccess;
+cudaError_t launch_copy_rows(const void* src, void* dst, int64_t n0, int64_t n1, int64_t n2, int64_t d,
+                             const int64_t src_strides[3], const int64_t dst_strides[3], cudaStream_t stream) {
+  if (n0 * n1 * n2 * d == 0) return cudaSuccess;
+  bool vec = d % 8 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0;
+  for (int i = 0; i < 3; ++i) vec = vec && src_strides[i] % 8 == 0 && dst_strides[i] % 8 == 0;
+  const int64_t dv = vec ? d / 8 : d;
+  const int64_t total = n0 * n1 * n2 * dv;
   const unsigned grid = static_cast<unsigned>((total + 255) / 256);
-  pack_rows_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), total,
-                                             static_cast<int>(n1), static_cast<int>(n2), static_cast<int>(d), s0, s1, s2);
+  const uint16_t* s = static_cast<const uint16_t*>(src);
+  uint16_t* t = static_cast<uint16_t*>(dst);
+  if (vec)
+    copy_rows_kernel<8><<<grid, 256, 0, stream>>>(s, t, total, static_cast<int>(n1), static_cast<int>(n2), static_cast<int>(dv),
+                                                  src_strides[0], src_strides[1], src_strides[2], dst_strides[0],
+                                                  dst_strides[1], dst_strides[2]);
+  else
+    copy_rows_kernel<1><<<grid, 256, 0, stream>>>(s, t, total, static_cast<int>(n1), static_cast<int>(n2), static_cast<int>(dv),
+                                                  src_strides[0], src_strides[1], src_strides[2], dst_strides[0],
+                                                  dst_strides[1], dst_strides[2]);
   return cudaGetLastError();
 }
 

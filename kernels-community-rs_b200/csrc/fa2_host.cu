@@ -677,15 +677,22 @@ int fa2_layout_is_addressable(const void* ptr, const int64_t* outer_strides, int
   return 1;
 }
 
-int fa2_pack_16bit(const void* src, void* dst, const int64_t shape[4], const int64_t outer_strides[3], void* stream) {
-  if (src == nullptr || dst == nullptr) return fail(FA2_E_VALUE, "fa2_pack_16bit: null tensor");
+int fa2_copy_16bit(const void* src, const int64_t src_strides[3], void* dst, const int64_t dst_strides[3],
+                   const int64_t shape[4], void* stream) {
+  if (src == nullptr || dst == nullptr) return fail(FA2_E_VALUE, "fa2_copy_16bit: null tensor");
   for (int i = 0; i < 4; ++i)
-    if (shape[i] < 0 || shape[i] > INT32_MAX) return fail(FA2_E_VALUE, "fa2_pack_16bit: unsupported shape");
+    if (shape[i] < 0 || shape[i] > INT32_MAX) return fail(FA2_E_VALUE, "fa2_copy_16bit: unsupported shape");
   const DeviceScope scope(src);
-  cudaError_t e = fa2::launch_pack_rows(src, dst, shape[0], shape[1], shape[2], shape[3], outer_strides[0],
-                                        outer_strides[1], outer_strides[2], static_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "packing copy launch failed: %s", cudaGetErrorString(e));
+  cudaError_t e = fa2::launch_copy_rows(src, dst, shape[0], shape[1], shape[2], shape[3], src_strides, dst_strides,
+                                        static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "copy launch failed: %s", cudaGetErrorString(e));
   return FA2_OK;
+}
+
+int fa2_pack_16bit(const void* src, void* dst, const int64_t shape[4], const int64_t outer_strides[3], void* stream) {
+  if (shape == nullptr || outer_strides == nullptr) return fail(FA2_E_VALUE, "fa2_pack_16bit: null argument");
+  const int64_t packed[3] = {shape[1] * shape[2] * shape[3], shape[2] * shape[3], shape[3]};
+  return fa2_copy_16bit(src, outer_strides, dst, packed, shape, stream);
 }
 
 int fa2_bwd_static(const fa2_bwd_args* args, void* stream) { return bwd_static_impl(args, stream); }

@@ -15,9 +15,10 @@ cudaError_t launch_bwd(const BwdParams& p, int head_dim, bool bf16, int num_sms,
 // delta = rowsum(dO * O) into the padded layouts (dense [B,H,Sq_pad], packed [H,total_q+128*B]).
 cudaError_t launch_bwd_preprocess(const PreprocessParams& p, cudaStream_t stream);
 
+// Copy of a 16-bit [n0, n1, n2, d] tensor (unit last stride) between two layouts given by their outer element strides.
+cudaError_t launch_copy_rows(const void* src, void* dst, int64_t n0, int64_t n1, int64_t n2, int64_t d,
+                             const int64_t src_strides[3], const int64_t dst_strides[3], cudaStream_t stream);
 // dst(16-bit) = src(fp32) * scale over n elements (n a multiple of 8).
-cudaError_t launch_pack_rows(const void* src, void* dst, int64_t n0, int64_t n1, int64_t n2, int64_t d, int64_t s0,
-                             int64_t s1, int64_t s2, cudaStream_t stream);
 cudaError_t launch_dq_convert(const float* src, void* dst, int64_t n, float scale, bool bf16, cudaStream_t stream);
 
 }  // namespace fa2

@@ -18,9 +18,11 @@
 #include <tvm/ffi/function.h>
 #include <tvm/ffi/optional.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <string>
+#include <vector>
 
 #include "fa2_b200.h"
 
@@ -121,6 +123,69 @@ Tensor addressable(const Tensor& t, DLDevice dev) {
   return packed;
 }
 
+// ---- layout predicates of a caller-supplied output (the reference: host/layout.rs:127-172, 145-456)
+// Number of elements between the first and one past the last element of the view.
+uint64_t element_span(const Tensor& t) {
+  uint64_t span = 1;
+  for (int i = 0; i < t.ndim(); ++i) {
+    if (t.shape()[i] == 0) return 0;
+    span += static_cast<uint64_t>(t.shape()[i] - 1) * static_cast<uint64_t>(t.strides()[i]);
+  }
+  return span;
+}
+
+// Do the address ranges of two 16-bit tensors intersect?
+bool ranges_overlap(const Tensor& a, const Tensor& b) {
+  const uint64_t x = reinterpret_cast<uint64_t>(a.data_ptr()), y = reinterpret_cast<uint64_t>(b.data_ptr());
+  return x < y + element_span(b) * 2 && y < x + element_span(a) * 2;
+}
+
+// True when no two index tuples of the view name the same element. Strides that nest (every stride at least
+// the extent of the faster axes) prove it at once. Otherwise the axes above the contiguous run are
+// enumerated, up to a bound, and their offsets must keep at least that run's length apart; a view that is too
+// large for the bounded check is refused as "cannot be proved", like the reference refuses what its own
+// bounded checks cannot prove.
+bool elements_are_disjoint(const Tensor& t) {
+  std::vector<std::pair<int64_t, int64_t>> dims;  // (stride, extent) of the axes that matter
+  for (int i = 0; i < t.ndim(); ++i) {
+    if (t.shape()[i] == 0) return true;
+    if (t.strides()[i] < 0) return false;
+    if (t.shape()[i] > 1) dims.emplace_back(t.strides()[i], t.shape()[i]);
+  }
+  std::sort(dims.begin(), dims.end());
+  int64_t span = 1;
+  bool nested = true;
+  for (const auto& [stride, n] : dims) {
+    if (stride < span) {
+      nested = false;
+      break;
+    }
+    span += (n - 1) * stride;
+  }
+  if (nested) return true;
+  // the contiguous run at the bottom, then every other axis by enumeration
+  int64_t run = 1;
+  size_t i = 0;
+  while (i < dims.size() && dims[i].first == run) run *= dims[i++].second;
+  int64_t count = 1;
+  for (size_t j = i; j < dims.size(); ++j) {
+    if (dims[j].first <= 0) return false;
+    count *= dims[j].second;
+    if (count > (int64_t{1} << 22)) return false;
+  }
+  std::vector<int64_t> offsets{0};
+  offsets.reserve(static_cast<size_t>(count));
+  for (size_t j = i; j < dims.size(); ++j) {
+    const size_t before = offsets.size();
+    for (int64_t k = 1; k < dims[j].second; ++k)
+      for (size_t m = 0; m < before; ++m) offsets.push_back(offsets[m] + k * dims[j].first);
+  }
+  std::sort(offsets.begin(), offsets.end());
+  for (size_t m = 1; m < offsets.size(); ++m)
+    if (offsets[m] - offsets[m - 1] < run) return false;
+  return true;
+}
+
 void unsupported(const char* what) {
   TVM_FFI_THROW(ValueError) << what << " is not built in the sm_100a library";
 }
@@ -199,7 +264,20 @@ Any fwd_impl(const AnyView* args, int32_t n, bool lse_only) {
                 o.device().device_type == dev.device_type && o.device().device_id == dev.device_id;
     for (int i = 0; same && i < 4; ++i) same = o.shape()[i] == q.shape()[i];
     if (!same) TVM_FFI_THROW(ValueError) << "out must match q's shape, dtype and device";
-    if (o.strides()[3] != 1 && d > 1) TVM_FFI_THROW(ValueError) << "out must have unit last stride";
+    if ((o.strides()[3] != 1 && d > 1) || !elements_are_disjoint(o))
+      TVM_FFI_THROW(ValueError) << "out must have unit last stride and nonoverlapping non-negative strides; unsupported "
+                                   "writable layout: elements overlap or the bounded safety checks cannot prove they are "
+                                   "disjoint. Use a separately allocated contiguous output.";
+  }
+  // A supplied output is written in place when the kernels can address it and it shares no memory with an input;
+  // otherwise the result goes to a temporary and is copied into it afterwards (host/forward/mod.rs:367-375,832-840).
+  bool copy_out = false;
+  if (supplied.has_value()) {
+    const Tensor& o = supplied.value();
+    int64_t os[3] = {b > 1 ? o.strides()[0] : 0, sq > 1 ? o.strides()[1] : 0, h > 1 ? o.strides()[2] : 0};
+    copy_out = !fa2_layout_is_addressable(o.data_ptr(), os, 3) || ranges_overlap(o, q) || ranges_overlap(o, k) ||
+               ranges_overlap(o, v);
+    if (copy_out) out = alloc({b, sq, h, d}, q.dtype(), dev);
   }
   Tensor lse = alloc({b, h, sq}, kF32, dev);
 
@@ -227,6 +305,14 @@ Any fwd_impl(const AnyView* args, int32_t n, bool lse_only) {
   a.window_right = static_cast<int32_t>(wr);
   a.softcap = static_cast<float>(softcap);
   check(fa2_fwd(&a, stream_of(dev)));
+  if (copy_out) {
+    const Tensor& o = supplied.value();
+    const int64_t shape4[4] = {b, sq, h, d};
+    const int64_t from[3] = {sq * h * d, h * d, d};
+    const int64_t to[3] = {o.strides()[0], o.strides()[1], o.strides()[2]};
+    check(fa2_copy_16bit(out.data_ptr(), from, o.data_ptr(), to, shape4, stream_of(dev)));
+    out = o;
+  }
   if (lse_only) return Any(lse);
   if (n >= 14) return Any(Array<Tensor>{out, lse, alloc({0}, q.dtype(), dev)});
   return Any(Array<Tensor>{out, lse});

@@ -61,7 +61,7 @@ class BwdArgs(C.Structure):
 # Every symbol include/fa2_b200.h declares; the CPU test suite checks that the library exports them.
 EXPORTS = (
     "fa2_fwd", "fa2_varlen_fwd", "fa2_bwd_preprocess", "fa2_bwd_workspace_bytes", "fa2_bwd",
-    "fa2_bwd_static", "fa2_bwd_static_status", "fa2_layout_is_addressable", "fa2_pack_16bit",
+    "fa2_bwd_static", "fa2_bwd_static_status", "fa2_layout_is_addressable", "fa2_pack_16bit", "fa2_copy_16bit",
     "fa2_last_error", "fa2_device_status", "fa2_sm_count",
 )
 

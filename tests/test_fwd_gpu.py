@@ -256,3 +256,39 @@ def test_unaddressable_views_are_packed_by_the_operator_layer():
     tol = BWD_TOL[torch.float16]
     for got, ref in ((dq, dq_ref), (dk, dk_ref), (dv, dv_ref)):
         torch.testing.assert_close(got.float().cpu(), ref, atol=tol["atol"], rtol=tol["rtol"])
+
+
+def test_supplied_out_layouts():
+    """A caller-supplied `out` (flash-attn2-rs/src/host/forward/mod.rs:349-375, tests/test_gold.py:119-256): written
+    in place when the kernels can address it and it shares no memory with an input, otherwise through a
+    temporary and a copy; refused when its own elements overlap."""
+    import flash_attn2_b200 as fa
+
+    g = torch.Generator().manual_seed(5)
+    # rows outside a simple stride nesting: shape (2, 2049, 2, 16) with strides (40, 88, 64, 1)
+    q = torch.randn(2, 2049, 2, 16, generator=g).to(torch.float16).cuda()
+    kv = q[:, :1]
+    want = fa.fwd(q, kv, kv)[0]
+    out = torch.empty(180344, device="cuda", dtype=q.dtype).as_strided(q.shape, (40, 88, 64, 1))
+    got = fa.fwd(q, kv, kv, out=out)[0]
+    assert got.data_ptr() == out.data_ptr()
+    assert torch.equal(got, want)
+    # a base that is off by one element: computed aside and copied, the element in front stays untouched
+    q2 = torch.randn(2, 33, 4, 64, generator=g).to(torch.bfloat16).cuda()
+    k2 = torch.randn(2, 47, 2, 64, generator=g).to(torch.bfloat16).cuda()
+    want2 = fa.fwd(q2, k2, k2, is_causal=True)[0]
+    storage = torch.full((q2.numel() + 1,), 123.0, device="cuda", dtype=q2.dtype)
+    got2 = fa.fwd(q2, k2, k2, out=storage[1:].view(q2.shape), is_causal=True)[0]
+    assert storage[0] == 123 and torch.equal(got2, want2)
+    # out aliases q: the inputs must be read before anything is written over them
+    q3 = q2.clone()
+    got3 = fa.fwd(q3, k2, k2, out=q3, is_causal=True)[0]
+    assert got3.data_ptr() == q3.data_ptr() and torch.equal(got3, want2)
+    # a head-sliced view of a larger output is written in place
+    big = torch.zeros(2, 33, 8, 64, device="cuda", dtype=q2.dtype)
+    got4 = fa.fwd(q2, k2, k2, out=big[:, :, 2:6], is_causal=True)[0]
+    assert torch.equal(got4, want2) and (big[:, :, :2] == 0).all() and (big[:, :, 6:] == 0).all()
+    # elements that overlap each other cannot be a destination
+    bad = torch.empty(33 * 4 * 64, device="cuda", dtype=q2.dtype).as_strided(q2.shape, (0, 4 * 64, 64, 1))
+    with pytest.raises((ValueError, RuntimeError)):
+        fa.fwd(q2, k2, k2, out=bad)
