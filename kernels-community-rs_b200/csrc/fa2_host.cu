@@ -184,7 +184,6 @@ int fwd_common(const fa2_fwd_args* a, void* stream_v, bool packed) {
   const int d = a->head_dim;
   if (d > 256) return fail(FA2_E_VALUE, "head dim must be <= 256, got %d", d);
   if (d < 8 || d % 8 != 0) return fail(FA2_E_VALUE, "head_size must be a positive multiple of 8, got %d", d);
-  if (d > 128) return fail(FA2_E_VALUE, "head dim %d is not built for sm_100a yet (multiples of 8 up to 128 are)", d);
   if (a->heads_k <= 0 || a->heads % a->heads_k != 0)
     return fail(FA2_E_VALUE, "num_heads (%d) must be a multiple of num_heads_k (%d)", a->heads, a->heads_k);
   if (a->batch <= 0 || a->heads <= 0 || a->batch > 65535 || a->heads > 65535)
@@ -264,11 +263,13 @@ int fwd_common(const fa2_fwd_args* a, void* stream_v, bool packed) {
   if ((rc = make_map(&p.tm_q, a->q, a->dtype, 2, d, a->heads, rows_q, nbatch, a->q_stride[2], a->q_stride[1],
                      a->q_stride[0], 64, 128, "q")) != FA2_OK)
     return rc;
+  // Head dims above 128 run on the kernel with 64-key tiles (fwd_wide_sm100.cu); the others take 128 keys a tile.
+  const int kv_box_rows = d > 128 ? 64 : 128;
   if ((rc = make_map(&p.tm_k, a->k, a->dtype, 2, d, a->heads_k, rows_k, nbatch, a->k_stride[2], a->k_stride[1],
-                     a->k_stride[0], 64, 128, "k")) != FA2_OK)
+                     a->k_stride[0], 64, kv_box_rows, "k")) != FA2_OK)
     return rc;
   if ((rc = make_map(&p.tm_v, a->v, a->dtype, 2, d, a->heads_k, rows_k, nbatch, a->v_stride[2], a->v_stride[1],
-                     a->v_stride[0], 64, 128, "v")) != FA2_OK)
+                     a->v_stride[0], 64, kv_box_rows, "v")) != FA2_OK)
     return rc;
   if ((rc = make_map(&p.tm_o, a->out, a->dtype, 2, d, a->heads, rows_q, nbatch, a->o_stride[2], a->o_stride[1],
                      a->o_stride[0], 64, 128, "out")) != FA2_OK)
@@ -295,7 +296,8 @@ int fwd_common(const fa2_fwd_args* a, void* stream_v, bool packed) {
   p.status = rt->status;
 
   p.head_dim = d;
-  cudaError_t e = fa2::launch_fwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream);
+  cudaError_t e = d > 128 ? fa2::launch_fwd_wide(p, d, a->dtype == FA2_BF16, stream)
+                          : fa2::launch_fwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream);
   if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "forward launch failed: %s", cudaGetErrorString(e));
   return FA2_OK;
 }

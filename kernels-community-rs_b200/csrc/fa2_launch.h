@@ -8,6 +8,10 @@ namespace fa2 {
 // Dense and packed (varlen) forward; head_dim is a multiple of 8 up to 128 (kernels for D = 64 and 128).
 cudaError_t launch_fwd(const FwdParams& p, int head_dim, bool bf16, int num_sms, cudaStream_t stream);
 
+// The same for head_dim a multiple of 8 in 136..256: one CTA per 128-row query block, 64-key tiles; p.tm_k and
+// p.tm_v carry boxes of 64 rows.
+cudaError_t launch_fwd_wide(const FwdParams& p, int head_dim, bool bf16, cudaStream_t stream);
+
 // dQ / dK / dV for head_dim a multiple of 8 up to 128; the fp32 dQ accumulator behind p.tm_dqa (and the turn
 // counters p.dq_turn, when given) must be zero.
 cudaError_t launch_bwd(const BwdParams& p, int head_dim, bool bf16, int num_sms, cudaStream_t stream);

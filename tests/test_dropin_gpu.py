@@ -8,8 +8,8 @@ and a stand-in for the Hub loader. These tests run the copied test files in a ch
   * tests/test_fwd.py completely (18 parity cases against the crate's naive fp32 attention and
     3 rejection cases);
   * of tests/test_gold.py the forward cases that need only `flash_attn_func` of the gold kernel
-    (the flash_attn wheel of the image stands in for kernels-community/flash-attn2) and head dims
-    this library builds (multiples of 8 up to 128).
+    (the flash_attn wheel of the image stands in for kernels-community/flash-attn2), every head dim
+    of its parity list (8 ... 256).
 """
 import os
 import re
@@ -23,8 +23,6 @@ pytestmark = pytest.mark.gpu
 
 ROOT = Path(__file__).resolve().parent.parent
 REF = ROOT / "baseline" / "_ref"
-# head dims of test_gold.py's parity list that the sm_100a kernels do not cover
-UNBUILT_HEAD_DIMS = "d144 or d160 or d192 or d200 or d224 or d256"
 
 
 def _run(test_file, *extra):
@@ -52,6 +50,6 @@ def test_reference_package_runs_its_forward_tests_unmodified():
 
 def test_reference_gold_forward_cases_against_the_flash_attn_wheel():
     rc, tail = _run("test_gold.py", "-k",
-                    f"(test_forward_parity and not ({UNBUILT_HEAD_DIMS})) or test_strided_views or test_rejects_head_size")
+                    "test_forward_parity or test_strided_views or test_rejects_head_size")
     passed, failed = _counts(tail)
     assert rc == 0 and failed == 0 and passed >= 60, tail

@@ -134,6 +134,41 @@ def test_forward_empty_shapes():
     assert out.shape == (2, 0, 3, 128) and lse.shape == (2, 3, 0)
 
 
+WIDE_CASES = [
+    ("d256-full", 256, (1, 2, 2, 128, 128), {}),
+    ("d256-causal-gqa", 256, (2, 8, 2, 333, 333), dict(causal=True)),
+    ("d192-causal", 192, (2, 4, 4, 512, 512), dict(causal=True)),
+    ("d192-sq320-sk256-causal", 192, (1, 4, 4, 320, 256), dict(causal=True)),
+    ("d160-mqa-sq128-sk700", 160, (1, 4, 1, 128, 700), {}),
+    ("d136-window-wl64-wr64", 136, (1, 4, 4, 256, 256), dict(window_left=64, window_right=64)),
+    ("d256-local-causal-wl100-softcap", 256, (1, 4, 4, 300, 300), dict(causal=True, window_left=100, softcap=30.0)),
+    ("d192-alibi-causal", 192, (2, 4, 4, 256, 256), dict(causal=True, alibi=True)),
+    ("d256-alibi-full", 256, (1, 4, 4, 192, 192), dict(alibi=True)),
+    ("d224-negative-scale", 224, (1, 2, 2, 256, 256), dict(causal=True, softmax_scale=-0.08)),
+    ("d256-single-row", 256, (2, 4, 2, 1, 200), {}),
+    ("d192-rows-without-keys", 192, (1, 2, 2, 300, 100), dict(causal=True)),
+    ("d256-long", 256, (1, 2, 2, 1500, 2100), dict(causal=True)),
+]
+
+
+@pytest.mark.parametrize("name,d,shape,opt", WIDE_CASES, ids=[c[0] for c in WIDE_CASES])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["f16", "bf16"])
+def test_forward_head_dims_above_128(name, d, shape, opt, dtype):
+    """Head dims 136..256 (the reference's 192 and 256 buckets, flash-attn2-rs/src/host/tiles.rs:1) run on the
+    kernel with 64-key tiles; the cases repeat the masks and transforms of the D = 128 parity list."""
+    from flash_attn2_b200 import cabi_ops as ops
+    from oracle.attention_oracle import attention_forward
+
+    b, h, hk, sq, sk = shape
+    opt = dict(opt)
+    q, k, v = make_qkv(5, b, h, hk, sq, sk, d, dtype)
+    slopes = alibi_slopes(h) if opt.pop("alibi", False) else None
+    o_ref, lse_ref = attention_forward(q, k, v, alibi_slopes=slopes, **opt)
+    out, lse = ops.fwd(q.cuda(), k.cuda(), v.cuda(), alibi_slopes=None if slopes is None else slopes.cuda(), **opt)
+    assert ops.device_status() == 0
+    _check(out, lse, o_ref, lse_ref, dtype)
+
+
 def test_rejects_unsupported_inputs():
     """flash-attn2-rs/tests/test_fwd.py:172-181."""
     import flash_attn2_b200 as fa
@@ -210,6 +245,8 @@ TWICE_CASES = [
     ("B2 H4 S1024 D128 bf16 causal", 1, (2, 4, 4, 1024, 1024, 128), torch.bfloat16, dict(causal=True)),
     ("B2 H8/2 S512 D128 f16 causal", 1, (2, 8, 2, 512, 512, 128), torch.float16, dict(causal=True)),
     ("B1 H4 S777 D128 bf16 full", 1, (1, 4, 4, 777, 777, 128), torch.bfloat16, {}),
+    ("B2 H4 S1024 D256 bf16 causal", 1, (2, 4, 4, 1024, 1024, 256), torch.bfloat16, dict(causal=True)),
+    ("B1 H8/2 S640 D192 f16 full", 1, (1, 8, 2, 640, 640, 192), torch.float16, {}),
 ]
 
 

@@ -194,6 +194,46 @@ def test_varlen_other_head_dim_ragged():
     assert (guard == 7.0).all()
 
 
+@pytest.mark.parametrize("d", [192, 256, 160])
+@pytest.mark.parametrize("name,lq,lk,h,hk,opt", VARLEN_CASES, ids=[c[0] for c in VARLEN_CASES])
+def test_varlen_forward_head_dims_above_128(name, lq, lk, h, hk, opt, d):
+    """The packed forward for head dims 136..256, with a guard row behind the output (ragged tiles store by
+    predicate and must stop at the real head dim and at the end of the sequence)."""
+    from flash_attn2_b200 import cabi_ops as ops
+    from oracle.attention_oracle import varlen_forward
+
+    q, k, v, cu_q, cu_k = _packed(7, lq, lk, h, hk, d, torch.bfloat16)
+    o_ref, lse_ref = varlen_forward(q, k, v, cu_q, cu_k, **opt)
+    out, lse = ops.varlen_fwd(q.cuda(), k.cuda(), v.cuda(), cu_q.cuda(), cu_k.cuda(), max(lq), max(lk), **opt)
+    assert ops.device_status() == 0
+    assert lse.shape == (h, sum(lq))
+    _fwd_close(out, lse, o_ref, lse_ref, torch.bfloat16)
+
+
+def test_rows_after_a_packed_sequence_do_not_leak_head_dim_256():
+    """The NaN-neighbour test below for the forward kernel of the wide head dims."""
+    from flash_attn2_b200 import cabi_ops as ops
+
+    lengths = [130, 77, 257, 40, 300, 64]
+    q, k, v, cu, _ = _packed(5, lengths, lengths, 4, 2, 256, torch.bfloat16)
+    cc = cu.cuda()
+
+    def run(poison):
+        ts = [t.clone() for t in (q, k, v)]
+        if poison:
+            for i in (1, 3, 5):
+                for t in ts:
+                    t[int(cu[i]):int(cu[i + 1])] = float("nan")
+        out, lse = ops.varlen_fwd(*[t.cuda() for t in ts], cc, cc, max(lengths), max(lengths), causal=True)
+        assert ops.device_status() == 0
+        return out, lse
+
+    base, bad = run(False), run(True)
+    for i in (0, 2, 4):
+        a, b = int(cu[i]), int(cu[i + 1])
+        assert torch.equal(base[0][a:b], bad[0][a:b]) and torch.equal(base[1][:, a:b], bad[1][:, a:b]), i
+
+
 def test_rows_after_a_packed_sequence_do_not_leak():
     """The reference zero-fills the rows of a tile that lie past the end of a sequence
     (flash-attn2-rs/src/device/forward/mod.rs:171-175,200), so what a neighbouring sequence holds can
