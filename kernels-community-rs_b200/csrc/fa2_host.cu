@@ -681,9 +681,13 @@ int fa2_layout_is_addressable(const void* ptr, const int64_t* outer_strides, int
 
 int fa2_copy_16bit(const void* src, const int64_t src_strides[3], void* dst, const int64_t dst_strides[3],
                    const int64_t shape[4], void* stream) {
-  if (src == nullptr || dst == nullptr) return fail(FA2_E_VALUE, "fa2_copy_16bit: null tensor");
+  if (shape == nullptr || src_strides == nullptr || dst_strides == nullptr)
+    return fail(FA2_E_VALUE, "fa2_copy_16bit: null argument");
   for (int i = 0; i < 4; ++i)
     if (shape[i] < 0 || shape[i] > INT32_MAX) return fail(FA2_E_VALUE, "fa2_copy_16bit: unsupported shape");
+  // An empty tensor has nothing to copy and may come without storage.
+  if (shape[0] == 0 || shape[1] == 0 || shape[2] == 0 || shape[3] == 0) return FA2_OK;
+  if (src == nullptr || dst == nullptr) return fail(FA2_E_VALUE, "fa2_copy_16bit: null tensor");
   const DeviceScope scope(src);
   cudaError_t e = fa2::launch_copy_rows(src, dst, shape[0], shape[1], shape[2], shape[3], src_strides, dst_strides,
                                         static_cast<cudaStream_t>(stream));

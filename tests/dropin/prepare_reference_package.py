@@ -41,15 +41,59 @@ def torch_add_op_namespace_prefix(name: str) -> str:
 
 KERNELS_PY = '''"""Stand-in for the Hugging Face `kernels` loader: returns the local copy of the reference package."""
 import importlib
+import types
+
+
+def _gold():
+    """The "gold" kernel of test_gold.py (kernels-community/flash-attn2): the flash_attn wheel of this image,
+    which wraps the same FA2 CUDA kernels. Its Python module has the flash_attn_func family; the raw operators
+    the Hub package also exports (fwd, bwd, varlen_fwd, varlen_bwd: keyword forms of the extension's positional
+    entry points) are added here."""
+    iface = importlib.import_module("flash_attn.flash_attn_interface")
+    ext = importlib.import_module("flash_attn_2_cuda")
+    gold = types.ModuleType("flash_attn2_gold")
+    gold.__dict__.update({k: v for k, v in vars(iface).items() if not k.startswith("__")})
+
+    def scale_of(q, softmax_scale):
+        return q.shape[-1] ** -0.5 if softmax_scale is None else softmax_scale
+
+    def fwd(q, k, v, out=None, alibi_slopes=None, p_dropout=0.0, softmax_scale=None, is_causal=False,
+            window_size_left=-1, window_size_right=-1, softcap=0.0, return_softmax=False, gen=None):
+        return ext.fwd(q, k, v, out, alibi_slopes, p_dropout, scale_of(q, softmax_scale), is_causal,
+                       window_size_left, window_size_right, softcap, return_softmax, gen)
+
+    def bwd(dout, q, k, v, out, softmax_lse, dq=None, dk=None, dv=None, alibi_slopes=None, p_dropout=0.0,
+            softmax_scale=None, is_causal=False, window_size_left=-1, window_size_right=-1, softcap=0.0,
+            deterministic=False, gen=None, rng_state=None):
+        return ext.bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, alibi_slopes, p_dropout,
+                       scale_of(q, softmax_scale), is_causal, window_size_left, window_size_right, softcap,
+                       deterministic, gen, rng_state)
+
+    def varlen_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, out=None, seqused_k=None, leftpad_k=None, block_table=None,
+                   alibi_slopes=None, max_seqlen_q=0, max_seqlen_k=0, p_dropout=0.0, softmax_scale=None,
+                   zero_tensors=False, is_causal=False, window_size_left=-1, window_size_right=-1, softcap=0.0,
+                   return_softmax=False, gen=None):
+        return ext.varlen_fwd(q, k, v, out, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k, block_table,
+                              alibi_slopes, max_seqlen_q, max_seqlen_k, p_dropout, scale_of(q, softmax_scale),
+                              zero_tensors, is_causal, window_size_left, window_size_right, softcap, return_softmax, gen)
+
+    def varlen_bwd(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k, dq=None, dk=None, dv=None,
+                   alibi_slopes=None, max_seqlen_q=0, max_seqlen_k=0, p_dropout=0.0, softmax_scale=None,
+                   zero_tensors=False, is_causal=False, window_size_left=-1, window_size_right=-1, softcap=0.0,
+                   deterministic=False, gen=None, rng_state=None):
+        return ext.varlen_bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k, alibi_slopes,
+                              max_seqlen_q, max_seqlen_k, p_dropout, scale_of(q, softmax_scale), zero_tensors,
+                              is_causal, window_size_left, window_size_right, softcap, deterministic, gen, rng_state)
+
+    gold.fwd, gold.bwd, gold.varlen_fwd, gold.varlen_bwd = fwd, bwd, varlen_fwd, varlen_bwd
+    return gold
 
 
 def get_kernel(repo_id, version=None, revision=None, **_):
     if "flash-attn2-rs" in repo_id:
         return importlib.import_module("flash_attn2_rs")
     if repo_id.endswith("/flash-attn2"):
-        # The "gold" kernel of test_gold.py: the flash_attn wheel of this image has the same
-        # flash_attn_func / flash_attn_varlen_func surface (not its raw fwd / bwd operators).
-        return importlib.import_module("flash_attn.flash_attn_interface")
+        return _gold()
     raise ValueError(f"no local stand-in for {repo_id}")
 '''
 

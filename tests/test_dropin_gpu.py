@@ -7,9 +7,10 @@ and a stand-in for the Hub loader. These tests run the copied test files in a ch
 
   * tests/test_fwd.py completely (18 parity cases against the crate's naive fp32 attention and
     3 rejection cases);
-  * of tests/test_gold.py the forward cases that need only `flash_attn_func` of the gold kernel
-    (the flash_attn wheel of the image stands in for kernels-community/flash-attn2), every head dim
-    of its parity list (8 ... 256).
+  * of tests/test_gold.py the forward parity list (every head dim, 8 ... 256), and the layout, validation,
+    backward and packed cases inside this library's scope; the flash_attn wheel of the image stands in
+    for the gold kernel kernels-community/flash-attn2 (same FA2 CUDA kernels; the stand-in loader adds
+    the keyword forms of its raw operators).
 """
 import os
 import re
@@ -53,3 +54,17 @@ def test_reference_gold_forward_cases_against_the_flash_attn_wheel():
                     "test_forward_parity or test_strided_views or test_rejects_head_size")
     passed, failed = _counts(tail)
     assert rc == 0 and failed == 0 and passed >= 60, tail
+
+
+def test_reference_gold_layout_backward_and_packed_cases():
+    """The rest of test_gold.py that this library's scope covers and this torch can run: supplied and strided
+    outputs, empty keys, argument validation and conversion order, the batch-and-heads grid, strided backward
+    inputs against the gold backward, the packed forward + backward pair, an empty packed output, grouped decode
+    LSE. Left out by name: KV-cache, paged and dropout cases (not built) and `torch.compile`; the cases
+    parametrised over the gold module itself check that module, not this one. The file skips by itself what
+    needs `torch.Generator.philox_state`."""
+    rc, tail = _run("test_gold.py", "-k",
+                    "not kvcache and not paged and not dropout and not compiled and not test_forward_parity "
+                    "and not test_strided_views and not test_rejects_head_size and (flash-attn2-rs or not flash-attn2)")
+    passed, failed = _counts(tail)
+    assert rc == 0 and failed == 0 and passed >= 11, tail
