@@ -24,7 +24,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC,-fvisibility=hidden",
 ]
 
-KERNEL_SOURCES = ["fwd_sm100.cu", "fwd_wide_sm100.cu", "bwd_sm100.cu", "bwd_aux.cu", "fa2_host.cu"]
+KERNEL_SOURCES = ["fwd_sm100.cu", "fwd_wide_sm100.cu", "bwd_sm100.cu", "bwd_wide_sm100.cu", "bwd_aux.cu", "fa2_host.cu"]
 
 
 def _newer(target: Path, deps: list[Path]) -> bool:

@@ -371,8 +371,6 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
   const bool packed = a->cu_seqlens_q != nullptr;
   const int d = a->head_dim;
   if (d > 256 || d < 8 || d % 8 != 0) return fail(FA2_E_VALUE, "unsupported backward tensor dimensions");
-  if (d < 8 || d % 8 != 0 || d > 128)
-    return fail(FA2_E_VALUE, "head dim %d is not built for sm_100a yet (multiples of 8 up to 128 are)", d);
   if (a->heads_k <= 0 || a->heads % a->heads_k != 0)
     return fail(FA2_E_VALUE, "num_heads (%d) must be a multiple of num_heads_k (%d)", a->heads, a->heads_k);
   if (a->batch <= 0 || a->heads <= 0 || a->batch > 65535 || a->heads > 65535 || a->seqlen_q < 0 || a->seqlen_k < 0)
@@ -421,10 +419,13 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
   fa2::BwdParams p;
   memset(&p, 0, sizeof(p));
   const int64_t hd = static_cast<int64_t>(a->heads) * d, hkd = static_cast<int64_t>(a->heads_k) * d;
+  // Head dims above 128 run on the kernel that takes query rows 64 at a time (bwd_wide_sm100.cu).
+  const bool wide = d > 128;
+  const int q_box_rows = wide ? 64 : 128;
   if ((rc = make_map(&p.tm_q, a->q, a->dtype, 2, d, a->heads, rows_q, nbatch, a->q_stride[2], a->q_stride[1],
-                     a->q_stride[0], 64, 128, "q")) != FA2_OK) return rc;
+                     a->q_stride[0], 64, q_box_rows, "q")) != FA2_OK) return rc;
   if ((rc = make_map(&p.tm_do, a->dout, a->dtype, 2, d, a->heads, rows_q, nbatch, a->do_stride[2], a->do_stride[1],
-                     a->do_stride[0], 64, 128, "dout")) != FA2_OK) return rc;
+                     a->do_stride[0], 64, q_box_rows, "dout")) != FA2_OK) return rc;
   if ((rc = make_map(&p.tm_k, a->k, a->dtype, 2, d, a->heads_k, rows_k, nbatch, a->k_stride[2], a->k_stride[1],
                      a->k_stride[0], 64, 128, "k")) != FA2_OK) return rc;
   if ((rc = make_map(&p.tm_v, a->v, a->dtype, 2, d, a->heads_k, rows_k, nbatch, a->v_stride[2], a->v_stride[1],
@@ -485,14 +486,17 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
   // registers in key order) accumulates in a fixed key-block order when the workspace holds the
   // turn counters; otherwise, and in the combined call, the adds land in arrival order.
   const int64_t acc_bytes = bwd_accum_bytes(a), n_turn = bwd_turn_counters(a);
-  const bool ordered = a->which == 1 && a->dq_accum_bytes >= acc_bytes + n_turn * 4;
+  const bool ordered = !wide && a->which == 1 && a->dq_accum_bytes >= acc_bytes + n_turn * 4;
   p.dq_turn = ordered ? reinterpret_cast<int*>(static_cast<char*>(a->dq_accum) + acc_bytes) : nullptr;
   p.num_mblk_q = (a->seqlen_q + 127) / 128;
   if (want_dq && (e = cudaMemsetAsync(a->dq_accum, 0, ordered ? acc_bytes + n_turn * 4 : n_dq * 4, stream)) != cudaSuccess)
     return fail(FA2_E_RUNTIME, "memset failed: %s", cudaGetErrorString(e));
   if (a->ev_kernel_start != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_kernel_start), stream);
   p.head_dim = d;
-  e = fa2::launch_bwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream);
+  p.dq_acc = static_cast<float*>(a->dq_accum);
+  p.dq_rows = rows_q;
+  e = wide ? fa2::launch_bwd_wide(p, d, a->dtype == FA2_BF16, stream)
+           : fa2::launch_bwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream);
   if (a->ev_kernel_stop != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_kernel_stop), stream);
   if (e != cudaSuccess) return fail(FA2_E_RUNTIME, "backward launch failed: %s", cudaGetErrorString(e));
   if (want_dq && (e = fa2::launch_dq_convert(static_cast<const float*>(a->dq_accum), a->dq, n_dq, a->softmax_scale,

@@ -16,6 +16,10 @@ cudaError_t launch_fwd_wide(const FwdParams& p, int head_dim, bool bf16, cudaStr
 // counters p.dq_turn, when given) must be zero.
 cudaError_t launch_bwd(const BwdParams& p, int head_dim, bool bf16, int num_sms, cudaStream_t stream);
 
+// The same for head_dim a multiple of 8 in 136..256: one CTA per (128 keys, half of the head dim), query blocks of
+// 64 rows; p.tm_q and p.tm_do carry boxes of 64 rows, dQ goes through p.dq_acc, dK and dV through p.dk_ptr / p.dv_ptr.
+cudaError_t launch_bwd_wide(const BwdParams& p, int head_dim, bool bf16, cudaStream_t stream);
+
 // delta = rowsum(dO * O) into the padded layouts (dense [B,H,Sq_pad], packed [H,total_q+128*B]).
 cudaError_t launch_bwd_preprocess(const PreprocessParams& p, cudaStream_t stream);
 

@@ -77,6 +77,10 @@ struct BwdParams {
   // same rows, so every element is summed in descending key-block order and dQ is bit-reproducible.
   int* dq_turn;
   int num_mblk_q;                       // ceil(seqlen_q / 128)
+  // The kernel for head dims above 128 adds into the accumulator with plain reductions:
+  // dq_acc[((batch * dq_rows + row) * heads + head) * head_dim + d], dq_rows rows per batch entry.
+  float* dq_acc;
+  int64_t dq_rows;
 };
 
 struct PreprocessParams {

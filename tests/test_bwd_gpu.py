@@ -61,6 +61,73 @@ def test_backward_parity_cabi(name, shape, opt, dtype):
     _close(dv, dv_ref, dtype, "dv")
 
 
+WIDE_CASES = [
+    ("d256-full-s128", (1, 2, 2, 128, 128, 256), {}, False),
+    ("d256-causal-gqa-odd", (2, 8, 2, 333, 333, 256), dict(causal=True), False),
+    ("d192-causal", (2, 4, 4, 512, 512, 192), dict(causal=True), False),
+    ("d192-mqa-sq320-sk256", (1, 4, 1, 320, 256, 192), dict(causal=True), False),
+    ("d160-full-sq128-sk700", (1, 4, 4, 128, 700, 160), {}, False),
+    ("d136-window-wl64-wr64", (1, 4, 4, 256, 256, 136), dict(window_left=64, window_right=64), False),
+    ("d256-local-causal-wl100", (1, 4, 4, 300, 300, 256), dict(causal=True, window_left=100), False),
+    ("d224-custom-scale", (1, 2, 2, 256, 256, 224), dict(causal=True, softmax_scale=0.05), False),
+    ("d256-softcap30-causal", (1, 4, 4, 256, 256, 256), dict(causal=True, softcap=30.0), False),
+    ("d192-alibi-causal-gqa", (2, 4, 2, 256, 256, 192), dict(causal=True), True),
+    ("d256-alibi-softcap-window", (1, 4, 4, 200, 333, 256), dict(window_left=64, window_right=32, softcap=20.0), True),
+    ("d256-rows-without-keys", (1, 2, 2, 384, 256, 256), dict(causal=True), False),
+    ("d256-s1024-causal", (1, 4, 4, 1024, 1024, 256), dict(causal=True), False),
+]
+
+
+@pytest.mark.parametrize("name,shape,opt,use_alibi", WIDE_CASES, ids=[c[0] for c in WIDE_CASES])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["f16", "bf16"])
+def test_backward_head_dims_above_128(name, shape, opt, use_alibi, dtype):
+    """Head dims 136..256 (the reference's 192 and 256 buckets) run on the kernel that splits the head dim of dK,
+    dV and dQ over two CTAs; the cases repeat the masks and score transforms of the lists above."""
+    from flash_attn2_b200 import cabi_ops as ops
+    from oracle.attention_oracle import attention_backward
+
+    b, h, hk, sq, sk, d = shape
+    q, k, v, do = make_qkv(11, b, h, hk, sq, sk, d, dtype, with_do=True)
+    slopes = (torch.arange(1, h + 1, dtype=torch.float32) * 0.05) if use_alibi else None
+    sl_gpu = None if slopes is None else slopes.cuda()
+    qc, kc, vc, doc = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    out, lse = ops.fwd(qc, kc, vc, alibi_slopes=sl_gpu, **opt)
+    delta = ops.bwd_preprocess(doc, out)
+    dq, dk, dv = ops.bwd(qc, kc, vc, doc, lse, delta, alibi_slopes=sl_gpu, **opt)
+    assert ops.device_status() == 0
+    dq_ref, dk_ref, dv_ref, delta_ref = attention_backward(q, k, v, do, out=out.float().cpu(), alibi_slopes=slopes, **opt)
+    torch.testing.assert_close(delta.cpu(), delta_ref, atol=2e-5, rtol=1e-5)
+    _close(dq, dq_ref, dtype, "dq")
+    _close(dk, dk_ref, dtype, "dk")
+    _close(dv, dv_ref, dtype, "dv")
+    if "rows-without-keys" in name:
+        assert torch.isposinf(lse[:, :, :128]).all() and (dq[:, :128] == 0).all()
+
+
+def test_backward_head_dim_256_dq_only_dkv_only_and_autograd():
+    """The deterministic pair of the reference (bwd_dq + bwd_dkv) and the autograd surface at head dim 256."""
+    import flash_attn2_b200 as fa
+    from flash_attn2_b200 import cabi_ops as ops
+    from oracle.attention_oracle import attention_backward
+
+    q, k, v, do = make_qkv(12, 2, 4, 2, 300, 300, 256, torch.bfloat16, with_do=True)
+    qc, kc, vc, doc = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    out, lse = ops.fwd(qc, kc, vc, causal=True)
+    delta = ops.bwd_preprocess(doc, out)
+    dq, dk, dv = ops.bwd(qc, kc, vc, doc, lse, delta, causal=True)
+    dq1, _, _ = ops.bwd(qc, kc, vc, doc, lse, delta, causal=True, which=1)
+    _, dk2, dv2 = ops.bwd(qc, kc, vc, doc, lse, delta, causal=True, which=2)
+    assert ops.device_status() == 0
+    torch.testing.assert_close(dq1.float(), dq.float(), atol=2e-2, rtol=2e-2)  # arrival order differs run to run
+    assert torch.equal(dk2, dk) and torch.equal(dv2, dv)
+    qa, ka, va = (t.clone().requires_grad_() for t in (qc, kc, vc))
+    fa.flash_attn_func(qa, ka, va, causal=True).backward(doc)
+    gq, gk, gv, _ = attention_backward(q, k, v, do, causal=True)
+    _close(qa.grad, gq, torch.bfloat16, "dq")
+    _close(ka.grad, gk, torch.bfloat16, "dk")
+    _close(va.grad, gv, torch.bfloat16, "dv")
+
+
 def test_backward_rows_without_keys_get_zero_gradient():
     """Causal with Sq > Sk: the first Sq - Sk rows see no key (LSE = +inf) and must get dQ = 0."""
     q, k, v, do = make_qkv(3, 1, 2, 2, 384, 256, 128, torch.float16, with_do=True)
@@ -273,6 +340,8 @@ TWICE_BWD_CASES = [
     ("B2 H4 S1024 D128 bf16 causal", (2, 4, 4, 1024, 1024, 128), torch.bfloat16, True),
     ("B2 H8/2 S512 D128 f16 causal", (2, 8, 2, 512, 512, 128), torch.float16, True),
     ("B1 H4 S640 D64 bf16 full", (1, 4, 4, 640, 640, 64), torch.bfloat16, False),
+    ("B1 H4 S768 D256 bf16 causal", (1, 4, 4, 768, 768, 256), torch.bfloat16, True),
+    ("B1 H8/2 S512 D192 f16 full", (1, 8, 2, 512, 512, 192), torch.float16, False),
 ]
 
 

@@ -59,7 +59,7 @@ def test_varlen_forward_parity(name, lq, lk, h, hk, opt, dtype):
     _fwd_close(out, lse, o_ref, lse_ref, dtype)
 
 
-@pytest.mark.parametrize("name,lq,lk,h,hk,opt", VARLEN_CASES[:4], ids=[c[0] for c in VARLEN_CASES[:4]])
+@pytest.mark.parametrize("name,lq,lk,h,hk,opt", VARLEN_CASES[:5], ids=[c[0] for c in VARLEN_CASES[:5]])
 def test_varlen_backward_parity(name, lq, lk, h, hk, opt):
     from flash_attn2_b200 import cabi_ops as ops
     from oracle.attention_oracle import varlen_backward
@@ -210,28 +210,55 @@ def test_varlen_forward_head_dims_above_128(name, lq, lk, h, hk, opt, d):
     _fwd_close(out, lse, o_ref, lse_ref, torch.bfloat16)
 
 
+@pytest.mark.parametrize("d", [192, 256])
+@pytest.mark.parametrize("name,lq,lk,h,hk,opt", VARLEN_CASES[:5], ids=[c[0] for c in VARLEN_CASES[:5]])
+def test_varlen_backward_head_dims_above_128(name, lq, lk, h, hk, opt, d):
+    from flash_attn2_b200 import cabi_ops as ops
+    from oracle.attention_oracle import varlen_backward
+
+    q, k, v, cu_q, cu_k, do = _packed(8, lq, lk, h, hk, d, torch.bfloat16, with_do=True)
+    qc, kc, vc, doc, cq, ck = q.cuda(), k.cuda(), v.cuda(), do.cuda(), cu_q.cuda(), cu_k.cuda()
+    out, lse = ops.varlen_fwd(qc, kc, vc, cq, ck, max(lq), max(lk), **opt)
+    delta = ops.bwd_preprocess(doc, out, cu_seqlens_q=cq, max_seqlen_q=max(lq))
+    dq, dk, dv = ops.bwd(qc, kc, vc, doc, lse, delta, cu_seqlens_q=cq, cu_seqlens_k=ck, max_seqlen_q=max(lq),
+                         max_seqlen_k=max(lk), **opt)
+    assert ops.device_status() == 0
+    dq_ref, dk_ref, dv_ref, _ = varlen_backward(q, k, v, do, cu_q, cu_k, out=out.float().cpu(), lse=lse.cpu(), **opt)
+    tol = BWD_TOL[torch.bfloat16]
+    for got, ref in ((dq, dq_ref), (dk, dk_ref), (dv, dv_ref)):
+        assert torch.isfinite(got.float()).all()
+        torch.testing.assert_close(got.float().cpu(), ref, atol=tol["atol"], rtol=tol["rtol"])
+
+
 def test_rows_after_a_packed_sequence_do_not_leak_head_dim_256():
-    """The NaN-neighbour test below for the forward kernel of the wide head dims."""
+    """The NaN-neighbour test below for the kernels of the wide head dims (forward and backward)."""
     from flash_attn2_b200 import cabi_ops as ops
 
     lengths = [130, 77, 257, 40, 300, 64]
-    q, k, v, cu, _ = _packed(5, lengths, lengths, 4, 2, 256, torch.bfloat16)
+    q, k, v, cu, _, do = _packed(5, lengths, lengths, 4, 2, 256, torch.bfloat16, with_do=True)
     cc = cu.cuda()
 
     def run(poison):
-        ts = [t.clone() for t in (q, k, v)]
+        ts = [t.clone() for t in (q, k, v, do)]
         if poison:
             for i in (1, 3, 5):
                 for t in ts:
                     t[int(cu[i]):int(cu[i + 1])] = float("nan")
-        out, lse = ops.varlen_fwd(*[t.cuda() for t in ts], cc, cc, max(lengths), max(lengths), causal=True)
+        qc, kc, vc, doc = [t.cuda() for t in ts]
+        out, lse = ops.varlen_fwd(qc, kc, vc, cc, cc, max(lengths), max(lengths), causal=True)
+        delta = ops.bwd_preprocess(doc, out, cu_seqlens_q=cc, max_seqlen_q=max(lengths))
+        dq, dk, dv = ops.bwd(qc, kc, vc, doc, lse, delta, cu_seqlens_q=cc, cu_seqlens_k=cc,
+                             max_seqlen_q=max(lengths), max_seqlen_k=max(lengths), causal=True)
         assert ops.device_status() == 0
-        return out, lse
+        return out, lse, dq, dk, dv
 
     base, bad = run(False), run(True)
     for i in (0, 2, 4):
         a, b = int(cu[i]), int(cu[i + 1])
         assert torch.equal(base[0][a:b], bad[0][a:b]) and torch.equal(base[1][:, a:b], bad[1][:, a:b]), i
+        assert torch.equal(base[3][a:b], bad[3][a:b]) and torch.equal(base[4][a:b], bad[4][a:b]), i
+        assert torch.isfinite(bad[2][a:b].float()).all()
+        torch.testing.assert_close(bad[2][a:b].float(), base[2][a:b].float(), atol=2e-2, rtol=2e-2)
 
 
 def test_rows_after_a_packed_sequence_do_not_leak():
