@@ -37,7 +37,9 @@ extern "C" {
 #define FA2_E_RUNTIME (-3) /* CUDA failure, or a kernel reported a stalled pipeline */
 
 /* Strides are in elements: {batch, row, head}; the head_dim stride is 1. In packed mode
- * the batch stride is ignored. */
+ * the batch stride is ignored. head_dim is a multiple of 8 up to 256, the reference's range
+ * (flash-attn2-rs/src/host/tiles.rs:1): up to 128 on the two-stage kernels, above on kernels with
+ * smaller tiles (fwd_wide_sm100.cu, bwd_wide_sm100.cu). */
 typedef struct fa2_fwd_args {
   const void* q;
   const void* k;
@@ -95,7 +97,8 @@ FA2_API int fa2_bwd_preprocess(const fa2_bwd_preprocess_args* args, void* stream
  * turn counter per 32 query rows of every (batch, head). With them a dQ-only call (which = 1, the
  * deterministic bwd_dq of the reference) adds the key blocks' contributions in a fixed order, so dQ
  * is bit-reproducible; a workspace that only holds the accumulator is accepted too (arrival order).
- * dK and dV never use atomics and are always bit-reproducible.
+ * dK and dV never use atomics and are always bit-reproducible. Head dims above 128 always add dQ in
+ * arrival order.
  * Replaces backward_component + the `backward` and `backward_kv` kernels
  * (flash-attn2-rs/src/host/backward.rs:14-566, src/device/backward/dq.rs:12-302,438-576,
  *  src/device/backward/dkv.rs:15-266,865-1012). */
@@ -165,7 +168,7 @@ FA2_API int fa2_copy_16bit(const void* src, const int64_t src_strides[3], void* 
  * cudaFree or an allocating library routine.
  *
  * Limits and rules:
- *  - dense tensors only, which = 3, and batch * seqlen_q * heads * head_dim must not exceed
+ *  - dense tensors only, which = 3, head_dim up to 128, and batch * seqlen_q * heads * head_dim must not exceed
  *    FA2_BWD_STATIC_MAX_ELEMENTS (4,194,304: a 16 MiB array that every GPU which loads the
  *    library holds until the process exits); larger problems are rejected with FA2_E_VALUE;
  *  - the first call on a device looks up the arrays' device addresses (cudaGetSymbolAddress, with
