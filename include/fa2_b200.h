@@ -98,7 +98,7 @@ FA2_API int fa2_bwd_preprocess(const fa2_bwd_preprocess_args* args, void* stream
  * deterministic bwd_dq of the reference) adds the key blocks' contributions in a fixed order, so dQ
  * is bit-reproducible; a workspace that only holds the accumulator is accepted too (arrival order).
  * dK and dV never use atomics and are always bit-reproducible. Head dims above 128 always add dQ in
- * arrival order.
+ * arrival order. A dQ-only call (which = 1) may pass dk = dv = NULL, a dK/dV-only call dq = dq_accum = NULL.
  * Replaces backward_component + the `backward` and `backward_kv` kernels
  * (flash-attn2-rs/src/host/backward.rs:14-566, src/device/backward/dq.rs:12-302,438-576,
  *  src/device/backward/dkv.rs:15-266,865-1012). */

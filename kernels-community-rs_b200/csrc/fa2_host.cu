@@ -405,7 +405,7 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
     if (reinterpret_cast<uintptr_t>(a->dq_accum) % 16 || reinterpret_cast<uintptr_t>(a->dq) % 16)
       return fail(FA2_E_VALUE, "dq and dq_accum must be 16-byte aligned");
   }
-  if (a->dk == nullptr || a->dv == nullptr) return fail(FA2_E_VALUE, "dk and dv must be non-null");
+  if (want_dkv && (a->dk == nullptr || a->dv == nullptr)) return fail(FA2_E_VALUE, "dk and dv must be non-null");
   if (a->lse == nullptr || a->delta == nullptr) return fail(FA2_E_VALUE, "lse and delta must be non-null");
   const int ns = packed ? 2 : 3;
   const int so = packed ? 1 : 0;
@@ -413,7 +413,7 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
   if ((rc = check_layout(a->k, a->k_stride + so, ns, "k")) != FA2_OK) return rc;
   if ((rc = check_layout(a->v, a->v_stride + so, ns, "v")) != FA2_OK) return rc;
   if ((rc = check_layout(a->dout, a->do_stride + so, ns, "dout")) != FA2_OK) return rc;
-  if (reinterpret_cast<uintptr_t>(a->dk) % 16 || reinterpret_cast<uintptr_t>(a->dv) % 16)
+  if (want_dkv && (reinterpret_cast<uintptr_t>(a->dk) % 16 || reinterpret_cast<uintptr_t>(a->dv) % 16))
     return fail(FA2_E_VALUE, "dk and dv must be 16-byte aligned");
 
   fa2::BwdParams p;
@@ -430,10 +430,15 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
                      a->k_stride[0], 64, 128, "k")) != FA2_OK) return rc;
   if ((rc = make_map(&p.tm_v, a->v, a->dtype, 2, d, a->heads_k, rows_k, nbatch, a->v_stride[2], a->v_stride[1],
                      a->v_stride[0], 64, 128, "v")) != FA2_OK) return rc;
-  if ((rc = make_map(&p.tm_dk, a->dk, a->dtype, 2, d, a->heads_k, rows_k, nbatch, d, hkd, rows_k * hkd, 64, 128,
-                     "dk")) != FA2_OK) return rc;
-  if ((rc = make_map(&p.tm_dv, a->dv, a->dtype, 2, d, a->heads_k, rows_k, nbatch, d, hkd, rows_k * hkd, 64, 128,
-                     "dv")) != FA2_OK) return rc;
+  if (want_dkv) {
+    if ((rc = make_map(&p.tm_dk, a->dk, a->dtype, 2, d, a->heads_k, rows_k, nbatch, d, hkd, rows_k * hkd, 64, 128,
+                       "dk")) != FA2_OK) return rc;
+    if ((rc = make_map(&p.tm_dv, a->dv, a->dtype, 2, d, a->heads_k, rows_k, nbatch, d, hkd, rows_k * hkd, 64, 128,
+                       "dv")) != FA2_OK) return rc;
+  } else {  // a dQ-only call writes neither: the kernels never touch these maps
+    p.tm_dk = p.tm_k;
+    p.tm_dv = p.tm_v;
+  }
   if (want_dq) {
     if ((rc = make_map(&p.tm_dqa, a->dq_accum, 2, 4, d, a->heads, rows_q, nbatch, d, hd, rows_q * hd, 32, 32,
                        "dq_accum")) != FA2_OK) return rc;

@@ -421,12 +421,18 @@ Any bwd_impl(const AnyView* args, int32_t n, int which) {
   a.which = which;
   // Gradients are allocated like the inputs (backward.rs:199-204); the fp32 dQ accumulator is a
   // workspace tensor from the same stream-ordered allocator.
-  Tensor dq = alloc({b, sq, h, d}, q.dtype(), dev);
-  Tensor dk = alloc({b, sk, hk, d}, k.dtype(), dev);
-  Tensor dv = alloc({b, sk, hk, d}, v.dtype(), dev);
-  a.dq = dq.data_ptr();
-  a.dk = dk.data_ptr();
-  a.dv = dv.data_ptr();
+  // Only what the call returns is allocated (bwd_dq: dQ; bwd_dkv: dK and dV).
+  Optional<Tensor> dq, dk, dv;
+  if (which & 1) {
+    dq = alloc({b, sq, h, d}, q.dtype(), dev);
+    a.dq = dq.value().data_ptr();
+  }
+  if (which & 2) {
+    dk = alloc({b, sk, hk, d}, k.dtype(), dev);
+    dv = alloc({b, sk, hk, d}, v.dtype(), dev);
+    a.dk = dk.value().data_ptr();
+    a.dv = dv.value().data_ptr();
+  }
   Optional<Tensor> accum;
   const int64_t ws = fa2_bwd_workspace_bytes(&a);
   if (ws > 0) {
@@ -435,9 +441,9 @@ Any bwd_impl(const AnyView* args, int32_t n, int which) {
     a.dq_accum_bytes = ws;
   }
   check(fa2_bwd(&a, stream_of(dev)));
-  if (which == 1) return Any(dq);
-  if (which == 2) return Any(Array<Tensor>{dk, dv});
-  return Any(Array<Tensor>{dq, dk, dv});
+  if (which == 1) return Any(dq.value());
+  if (which == 2) return Any(Array<Tensor>{dk.value(), dv.value()});
+  return Any(Array<Tensor>{dq.value(), dk.value(), dv.value()});
 }
 
 // ------------------------------------------------------------------------------------ packed (varlen)

@@ -38,6 +38,11 @@ def _strides3(t: torch.Tensor):
     return (C.c_int64 * 3)(0, t.stride(0), t.stride(1))
 
 
+def _alloc(shape, dtype, device):
+    """Every output and workspace of this module is allocated here (a test substitutes a canary-padded one)."""
+    return torch.empty(tuple(shape), dtype=dtype, device=device)
+
+
 def _check_last_stride(name, t):
     if t.stride(-1) != 1:
         raise ValueError(f"{name} must have unit last stride")
@@ -61,10 +66,10 @@ def fwd(q, k, v, *, out=None, alibi_slopes=None, softmax_scale=None, causal=Fals
         _check_last_stride(name, t)
     sk, hk = k.shape[1], k.shape[2]
     if out is None:
-        out = torch.empty((b, sq, h, d), dtype=q.dtype, device=q.device)
+        out = _alloc((b, sq, h, d), q.dtype, q.device)
     elif out.shape != q.shape or out.dtype != q.dtype or out.device != q.device:
         raise ValueError("out must match q's shape, dtype and device")
-    lse = torch.empty((b, h, sq), dtype=torch.float32, device=q.device)
+    lse = _alloc((b, h, sq), torch.float32, q.device)
     a = _cabi.FwdArgs()
     a.q, a.k, a.v, a.out, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
     if alibi_slopes is not None:
@@ -111,8 +116,8 @@ def varlen_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, 
     for name, t in (("q", q), ("k", k), ("v", v)):
         _check_last_stride(name, t)
     batch = cu_seqlens_q.numel() - 1
-    out = torch.empty_like(q, memory_format=torch.contiguous_format)
-    lse = torch.full((h, total_q), float("inf"), dtype=torch.float32, device=q.device)
+    out = _alloc(q.shape, q.dtype, q.device)
+    lse = _alloc((h, total_q), torch.float32, q.device).fill_(float("inf"))
     a = _cabi.FwdArgs()
     a.q, a.k, a.v, a.out, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
     if alibi_slopes is not None:
@@ -153,12 +158,12 @@ def bwd_preprocess(dout, out, *, cu_seqlens_q=None, max_seqlen_q=None):
     a.dtype = _dtype_code(dout)
     if cu_seqlens_q is None:
         b, sq, h, d = out.shape
-        delta = torch.empty((b, h, (sq + 127) // 128 * 128), dtype=torch.float32, device=out.device)
+        delta = _alloc((b, h, (sq + 127) // 128 * 128), torch.float32, out.device)
         a.batch, a.seqlen_q = b, sq
     else:
         total_q, h, d = out.shape
         b = cu_seqlens_q.numel() - 1
-        delta = torch.zeros((h, total_q + 128 * b), dtype=torch.float32, device=out.device)
+        delta = _alloc((h, total_q + 128 * b), torch.float32, out.device).zero_()
         a.batch, a.seqlen_q = b, int(max_seqlen_q)
         a.cu_seqlens_q, a.total_q = cu_seqlens_q.data_ptr(), total_q
     a.delta = delta.data_ptr()
@@ -202,9 +207,9 @@ def bwd(q, k, v, dout, lse, delta, *, softmax_scale=None, causal=False, window_l
         a.batch, a.seqlen_q, a.seqlen_k = b, sq, sk
         if tuple(lse.shape) != (b, h, sq) or tuple(delta.shape) != (b, h, (sq + 127) // 128 * 128):
             raise ValueError("lse must be [B, H, Sq] and delta [B, H, ceil(Sq/128)*128]")
-    dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
-    dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
-    dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+    dq = _alloc(q.shape, q.dtype, q.device)
+    dk = _alloc(k.shape, k.dtype, k.device)
+    dv = _alloc(v.shape, v.dtype, v.device)
     a.q, a.k, a.v, a.dout = q.data_ptr(), k.data_ptr(), v.data_ptr(), dout.data_ptr()
     a.lse, a.delta = lse.data_ptr(), delta.data_ptr()
     a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
@@ -231,7 +236,7 @@ def bwd(q, k, v, dout, lse, delta, *, softmax_scale=None, causal=False, window_l
     need = lib.fa2_bwd_workspace_bytes(C.byref(a))
     if need > 0:
         if dq_accum is None:
-            dq_accum = torch.empty(need // 4, dtype=torch.float32, device=q.device)
+            dq_accum = _alloc((need // 4,), torch.float32, q.device)
         a.dq_accum, a.dq_accum_bytes = dq_accum.data_ptr(), dq_accum.numel() * 4
     with torch.cuda.device(q.device):
         _cabi.check(lib.fa2_bwd(C.byref(a), _stream(q)))

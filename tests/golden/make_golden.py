@@ -1,7 +1,6 @@
 """Generates tests/golden/reference_attention.pt from the reference's own test oracle.
 
-Runs only where the reference checkout is mounted (its path is the first argument, default
-/root/reference). It imports `reference_attention` from flash-attn2-rs/tests/test_fwd.py — the
+Runs only where the reference checkout is mounted (its path is the one argument). It imports `reference_attention` from flash-attn2-rs/tests/test_fwd.py — the
 crate's test-harness naive attention — with a stub for the `kernels` loader that module needs at
 import time, evaluates it on small seeded CPU inputs that cover the mask / GQA / softcap / ALiBi /
 ragged cases of that file's PARITY_CASES, and stores inputs' seeds and the outputs. The oracle in
@@ -64,4 +63,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path to the reference checkout>")
+    main(sys.argv[1])

@@ -1,7 +1,7 @@
 """GPU parity of the backward path (delta preprocess, dQ/dK/dV) against the CPU oracle.
 
 Shapes follow the reference's backward tests (flash-attn2-rs/tests/test_gold.py:269-363: MHA/GQA,
-causal, odd lengths, strided inputs, delta parity at 2e-5) plus BASELINE configs[2] at full size.
+causal, odd lengths, strided inputs, delta parity at 2e-5) plus the benchmark's backward workload (B16 H16 S2048 D128 bf16 causal) at full size.
 """
 import pytest
 import torch
@@ -195,7 +195,7 @@ def test_backward_through_tvm_ffi_ops_and_autograd():
 
 
 def test_config3_full_size_slices_and_properties():
-    """BASELINE configs[2] (B16 H16 S2048 D128 bf16 causal, dO from seed 2) at full size: oracle on
+    """The benchmark's backward workload (B16 H16 S2048 D128 bf16 causal, dO from seed 2) at full size: oracle on
     sampled (batch, head) units; dV and dK/dQ are linear in dO; the last key's dK/dV only see the
     last query row."""
     from flash_attn2_b200 import cabi_ops as ops

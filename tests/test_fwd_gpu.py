@@ -1,7 +1,7 @@
 """GPU parity of the forward path against the CPU oracle, through the C ABI and the tvm-ffi ops.
 
 Cases follow the reference's forward test (flash-attn2-rs/tests/test_fwd.py:93-134: masks, GQA/MQA,
-Sq != Sk, windows, softcap, ALiBi, odd lengths; fp16, D = 128, seed 0) plus the BASELINE configs.
+Sq != Sk, windows, softcap, ALiBi, odd lengths; fp16, D = 128, seed 0) plus the benchmark's workloads at full size.
 Tolerances are the reference's own (tests/_cases.py).
 """
 from pathlib import Path
@@ -66,7 +66,7 @@ def test_forward_parity_cabi(name, shape, opt, dtype):
 
 
 def test_config1_d64_fp16_noncausal():
-    """BASELINE configs[0]: B1 H4 S128 D64 fp16, seed 0, scale 1/8."""
+    """The reference's own CPU-runnable case: B1 H4 S128 D64 fp16, seed 0, scale 1/8."""
     from flash_attn2_b200 import cabi_ops as ops
     from oracle.attention_oracle import attention_forward
 
@@ -210,7 +210,7 @@ def _full_size_inputs(seed, with_do=False):
 
 
 def test_config2_full_size_slices_and_properties():
-    """BASELINE configs[1] at full size: oracle on sampled (batch, head) units, plus properties
+    """The benchmark's forward workload (B16 H16 S2048 D128 bf16 causal, seed 1) at full size: oracle on sampled (batch, head) units, plus properties
     that need no oracle (V = 1 gives O = 1; O is linear in V; first row attends only key 0)."""
     from flash_attn2_b200 import cabi_ops as ops
     from oracle.attention_oracle import attention_forward

@@ -1,7 +1,7 @@
 """GPU parity of the packed (varlen) forward and backward against the CPU oracle.
 
 Follows the reference's packed tests (flash-attn2-rs/tests/test_gold.py:482-534: GQA, an empty
-sequence, delta of shape [H, total_q + 128 * batch]) and BASELINE configs[3] (32 sequences with
+sequence, delta of shape [H, total_q + 128 * batch]) and the packed benchmark workload (32 sequences with
 lengths uniform in [128, 4096] from seed 3, H_q = 32, H_kv = 8, D = 128, causal, bf16).
 """
 import pytest
@@ -197,8 +197,8 @@ def test_varlen_other_head_dim_ragged():
 @pytest.mark.parametrize("d", [192, 256, 160])
 @pytest.mark.parametrize("name,lq,lk,h,hk,opt", VARLEN_CASES, ids=[c[0] for c in VARLEN_CASES])
 def test_varlen_forward_head_dims_above_128(name, lq, lk, h, hk, opt, d):
-    """The packed forward for head dims 136..256, with a guard row behind the output (ragged tiles store by
-    predicate and must stop at the real head dim and at the end of the sequence)."""
+    """The packed forward for head dims 136..256 (ragged tiles store by predicate and must stop at the real
+    head dim and at the end of the sequence: the oracle comparison covers every row of the output)."""
     from flash_attn2_b200 import cabi_ops as ops
     from oracle.attention_oracle import varlen_forward
 
