@@ -224,6 +224,7 @@ __global__ void __launch_bounds__(kBWThreads, 1) bwd_wide_kernel(const __grid_co
     };
     const float inv_cap = (p.softcap > 0.f) ? p.scale / p.softcap : 0.f;
     const float cap_l2 = p.softcap * kBWLog2e;
+    const bool fancy = (p.softcap > 0.f) || (p.alibi != nullptr);
     WWalk w{0, 0};
     float stat_next = n_iter > 0 ? load_stat(w) : 0.f;
     for (int it = 0; it < n_iter; ++it) {
@@ -252,6 +253,18 @@ __global__ void __launch_bounds__(kBWThreads, 1) bwd_wide_kernel(const __grid_co
       if (kpos >= ti.sk) c_hi = -1;
       const float slope = (p.alibi != nullptr) ? p.alibi[ti.b * p.alibi_batch_stride + hq] * kBWLog2e : 0.f;
       float pr[kBQ];  // P times the derivative of the score transform: what goes on to dS
+      if (!fancy) {
+#pragma unroll
+        for (int i = 0; i < kBQ; i += 2) {
+          float pv0 = ex2(fmaf(__uint_as_float(sr[i]), p.scale_log2, -lse_s[i]));
+          float pv1 = ex2(fmaf(__uint_as_float(sr[i + 1]), p.scale_log2, -lse_s[i + 1]));
+          if (i < c_lo || i >= c_hi) pv0 = 0.f;
+          if (i + 1 < c_lo || i + 1 >= c_hi) pv1 = 0.f;
+          pr[i] = pv0;
+          pr[i + 1] = pv1;
+          sr[i / 2] = pack2<BF16>(pv0, pv1);
+        }
+      } else
 #pragma unroll
       for (int i = 0; i < kBQ; i += 2) {
         float pp[2];
@@ -453,10 +466,12 @@ __global__ void __launch_bounds__(kBWThreads, 1) bwd_wide_kernel(const __grid_co
     const int n_ks = (p.head_dim + 15) / 16;  // steps of 16 over the head dim; what TMA left past it is zero
     // [keys x q] = A[keys x d] B[q x d]^T, both K-major, over the head dim in steps of 16
     auto kmajor_pair = [&](uint32_t d_tmem, uint64_t a, uint64_t b) {
-      for (int ks = 0; ks < n_ks; ++ks) {
-        const uint32_t in_atom = (ks & 3) * 2;
-        mma_ss(d_tmem, a + (ks >> 2) * kAtomK16 + in_atom, b + (ks >> 2) * kAtomQ16 + in_atom, idesc_qk, ks > 0 ? 1u : 0u);
-      }
+      static_for<16>([&](auto ks) {  // compile-time operand offsets keep the issuing thread lean
+        constexpr uint32_t in_atom = (ks.value & 3) * 2;
+        if (ks.value < n_ks)
+          mma_ss_o<(ks.value >> 2) * kAtomK16 + in_atom, (ks.value >> 2) * kAtomQ16 + in_atom>(d_tmem, a, b, idesc_qk,
+                                                                                            ks.value > 0 ? 1u : 0u);
+      });
     };
     uint32_t n_ragged = 0;  // ragged Q / dO tiles seen so far: the parity of the fixer's barriers
     auto ragged_q = [&](int mi) { return packed && (ti.m_start + mi) * kBQ + kBQ > ti.sq; };

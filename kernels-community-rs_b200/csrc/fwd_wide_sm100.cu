@@ -212,6 +212,7 @@ __global__ void __launch_bounds__(kWThreads, 1) fwd_wide_kernel(const __grid_con
     if (p.alibi != nullptr) slope = p.alibi[ti.b * p.alibi_batch_stride + ti.h] * 1.4426950408889634f;
     const float inv_cap = (p.softcap > 0.f) ? p.scale / p.softcap : 0.f;
     const float cap_l2 = p.softcap * 1.4426950408889634f;
+    const bool fancy = (p.softcap > 0.f) || (p.alibi != nullptr);
     bool ok = true;
     for (int i = 0; i < n_tiles; ++i) {
       const int j = ti.nb + i;
@@ -226,15 +227,20 @@ __global__ void __launch_bounds__(kWThreads, 1) fwd_wide_kernel(const __grid_con
       mbar_arrive(&s_free[buf]);  // the scores live in registers from here on
       const int col0 = j * kWN;
       // Scores into the log2 domain: scale (or softcap), ALiBi, then the mask.
+      if (fancy) {
 #pragma unroll
-      for (int c = 0; c < kWN; ++c) {
-        float x = __uint_as_float(sr[c]);
-        x = (p.softcap > 0.f) ? cap_l2 * wide_tanh(x * inv_cap) : x * p.scale_log2;
-        if (p.alibi != nullptr) {
-          const int col = col0 + c;
-          x += p.causal_alibi ? slope * static_cast<float>(col) : -slope * fabsf(static_cast<float>(row + ti.off - col));
+        for (int c = 0; c < kWN; ++c) {
+          float x = __uint_as_float(sr[c]);
+          x = (p.softcap > 0.f) ? cap_l2 * wide_tanh(x * inv_cap) : x * p.scale_log2;
+          if (p.alibi != nullptr) {
+            const int col = col0 + c;
+            x += p.causal_alibi ? slope * static_cast<float>(col) : -slope * fabsf(static_cast<float>(row + ti.off - col));
+          }
+          sr[c] = __float_as_uint(x);
         }
-        sr[c] = __float_as_uint(x);
+      } else {
+#pragma unroll
+        for (int c = 0; c < kWN; ++c) sr[c] = __float_as_uint(__uint_as_float(sr[c]) * p.scale_log2);
       }
       {
         int hi = ti.sk;
@@ -442,11 +448,15 @@ __global__ void __launch_bounds__(kWThreads, 1) fwd_wide_kernel(const __grid_con
       if (!mbar_wait(&s_free[buf], ((i >> 1) & 1) ^ 1, ctl, kWaitMmaSFree)) return false;
       tc_fence_after();
       const uint64_t b = k_desc + slot * kTile16;
-      for (int ks = 0; ks < n_ks; ++ks) {
-        const uint32_t in_atom = (ks & 3) * 2;
-        mma_ss(t_s + buf * kWN, q_desc + (ks >> 2) * kAtomQ16 + in_atom, b + (ks >> 2) * kAtomKV16 + in_atom, idesc_qk,
-               ks > 0 ? 1u : 0u);
-      }
+      // Compile-time operand offsets: a rolled loop that builds descriptors costs the issuing thread about twice
+      // the 54 cycles such an MMA takes.
+      const uint32_t d_s = t_s + buf * kWN;
+      static_for<16>([&](auto ks) {
+        constexpr uint32_t in_atom = (ks.value & 3) * 2;
+        if (ks.value < n_ks)
+          mma_ss_o<(ks.value >> 2) * kAtomQ16 + in_atom, (ks.value >> 2) * kAtomKV16 + in_atom>(d_s, q_desc, b, idesc_qk,
+                                                                                             ks.value > 0 ? 1u : 0u);
+      });
       mma_commit(&s_full[buf]);
       advance();
       return true;
@@ -462,8 +472,9 @@ __global__ void __launch_bounds__(kWThreads, 1) fwd_wide_kernel(const __grid_con
       if (!mbar_wait(p_full, i & 1, ctl, kWaitMmaPFull)) return false;
       tc_fence_after();
       const uint64_t b = v_desc + slot * kTile16;
-#pragma unroll
-      for (int ks = 0; ks < kWN / 16; ++ks) mma_ss(t_o, p_desc + ks * 2, b + ks * (2048 >> 4), idesc_pv, (i == 0 && ks == 0) ? 0u : 1u);
+      static_for<kWN / 16>([&](auto ks) {
+        mma_ss_o<ks.value * 2, ks.value * (2048 >> 4)>(t_o, p_desc, b, idesc_pv, (i == 0 && ks.value == 0) ? 0u : 1u);
+      });
       mma_commit(pv_done);
       advance();
       return true;
