@@ -30,7 +30,8 @@ def _run(test_file, *extra):
     if not (REF / "flash_attn2_rs" / "__init__.py").exists():
         pytest.fail("baseline/_ref is missing: run tests/dropin/prepare_reference_package.py <reference checkout>")
     env = dict(os.environ, PYTHONPATH=str(REF))
-    cmd = [sys.executable, "-m", "pytest", str(REF / "tests" / test_file), "-q", "-p", "no:cacheprovider",
+    path = test_file if os.path.isabs(str(test_file)) else str(REF / "tests" / test_file)
+    cmd = [sys.executable, "-m", "pytest", path, "-q", "-p", "no:cacheprovider",
            "-W", "ignore::pytest.PytestUnknownMarkWarning", *extra]
     proc = subprocess.run(cmd, cwd=str(REF), env=env, capture_output=True, text=True, timeout=900)
     tail = (proc.stdout + proc.stderr)[-3000:]
@@ -68,3 +69,12 @@ def test_reference_gold_layout_backward_and_packed_cases():
                     "and not test_strided_views and not test_rejects_head_size and (flash-attn2-rs or not flash-attn2)")
     passed, failed = _counts(tail)
     assert rc == 0 and failed == 0 and passed >= 11, tail
+
+
+def test_reference_wrappers_autograd_and_compile():
+    """The reference package's six autograd wrappers (head size 63 padded by the wrapper, 128, and 200 on the
+    wide-head-dim kernels) and a torch.compile'd forward + backward through its registered custom ops, against
+    the gold kernel: tests/dropin/reference_wrappers_cases.py, run with the reference package on the path."""
+    rc, tail = _run(ROOT / "tests" / "dropin" / "reference_wrappers_cases.py", "--rootdir", str(REF))
+    passed, failed = _counts(tail)
+    assert rc == 0 and failed == 0 and passed == 19, tail
