@@ -28,36 +28,41 @@ __device__ __forceinline__ float2 unpack2(uint32_t w) {
 // is written as zero.
 constexpr int kRows = 4;
 
-template <bool BF16, int LANES>
+template <bool BF16, int LANES, typename IDX>
 __global__ void __launch_bounds__(256) preprocess_kernel(const PreprocessParams p) {
-  const int64_t group = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) / LANES;
+  // IDX is 32-bit whenever the number of (batch, row, head) units allows: the 64-bit divisions of the index
+  // arithmetic otherwise take longer than the loads they lead to.
+  const IDX group = static_cast<IDX>((blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x) / LANES);
   const int lane = threadIdx.x % LANES;
-  const int64_t total = static_cast<int64_t>(p.batch) * p.seqlen_pad * p.heads;
+  const IDX total = static_cast<IDX>(static_cast<uint64_t>(p.batch) * p.seqlen_pad * p.heads);
   const int chunks = p.head_dim / 8;  // 16-byte chunks per row; LANES >= chunks
   uint4 x[kRows], y[kRows];
   bool store[kRows];
   int64_t dst[kRows];
+  // The first unit is split into (batch, row, head) once; the following ones are reached by counting up.
+  const IDX gid0 = group * kRows;
+  const bool any = gid0 < total;
+  int h = static_cast<int>((any ? gid0 : 0) % static_cast<IDX>(p.heads));
+  const IDX bs0 = (any ? gid0 : 0) / static_cast<IDX>(p.heads);
+  int s = static_cast<int>(bs0 % static_cast<IDX>(p.seqlen_pad));
+  int b = static_cast<int>(bs0 / static_cast<IDX>(p.seqlen_pad));
   // No thread leaves before the shuffles below: a warp holds 32 / LANES groups, some of which may lie past
   // the end.
 #pragma unroll
   for (int r = 0; r < kRows; ++r) {
-    const int64_t gid = group * kRows + r;
-    const bool in_range = gid < total;
-    const int h = static_cast<int>((in_range ? gid : 0) % p.heads);
-    const int64_t bs = (in_range ? gid : 0) / p.heads;
-    const int s = static_cast<int>(bs % p.seqlen_pad);
-    const int b = static_cast<int>(bs / p.seqlen_pad);
+    const bool in_range = any && (gid0 + r < total);
     int64_t row = s;     // row inside the input tensors
     int64_t drow = s;    // row inside delta
     bool live = in_range && s < p.seqlen_q;
     store[r] = in_range;
     int bq = b;
     if (p.cu_q != nullptr) {
-      const int q0 = p.cu_q[b];
-      const int len = p.cu_q[b + 1] - q0;
+      const int bb = in_range ? b : 0;
+      const int q0 = p.cu_q[bb];
+      const int len = p.cu_q[bb + 1] - q0;
       live = in_range && s < len;
       row = q0 + s;
-      drow = q0 + 128 * b + s;
+      drow = q0 + 128 * bb + s;
       bq = 0;
       // Padding of a packed sequence: only the 128-row tail that belongs to it.
       if (s >= (len + 127) / 128 * 128) store[r] = false;
@@ -70,6 +75,13 @@ __global__ void __launch_bounds__(256) preprocess_kernel(const PreprocessParams 
                                             row * p.do_row_stride + h * p.do_head_stride)[lane];
       y[r] = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.out) + bq * p.o_batch_stride +
                                             row * p.o_row_stride + h * p.o_head_stride)[lane];
+    }
+    if (++h == p.heads) {
+      h = 0;
+      if (++s == p.seqlen_pad) {
+        s = 0;
+        ++b;
+      }
     }
   }
 #pragma unroll
@@ -119,15 +131,22 @@ cudaError_t launch_bwd_preprocess(const PreprocessParams& p, cudaStream_t stream
   const int lanes = p.head_dim <= 64 ? 8 : p.head_dim <= 128 ? 16 : 32;  // one 16-byte chunk of the row per lane
   const int64_t threads = groups * lanes;
   const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
+  const bool small = units < (1ll << 31);
+#define FA2_LAUNCH_PRE(BF, L)                                                      \
+  do {                                                                             \
+    if (small) preprocess_kernel<BF, L, uint32_t><<<grid, 256, 0, stream>>>(p);    \
+    else preprocess_kernel<BF, L, uint64_t><<<grid, 256, 0, stream>>>(p);          \
+  } while (0)
   if (p.bf16) {
-    if (lanes == 8) preprocess_kernel<true, 8><<<grid, 256, 0, stream>>>(p);
-    else if (lanes == 16) preprocess_kernel<true, 16><<<grid, 256, 0, stream>>>(p);
-    else preprocess_kernel<true, 32><<<grid, 256, 0, stream>>>(p);
+    if (lanes == 8) FA2_LAUNCH_PRE(true, 8);
+    else if (lanes == 16) FA2_LAUNCH_PRE(true, 16);
+    else FA2_LAUNCH_PRE(true, 32);
   } else {
-    if (lanes == 8) preprocess_kernel<false, 8><<<grid, 256, 0, stream>>>(p);
-    else if (lanes == 16) preprocess_kernel<false, 16><<<grid, 256, 0, stream>>>(p);
-    else preprocess_kernel<false, 32><<<grid, 256, 0, stream>>>(p);
+    if (lanes == 8) FA2_LAUNCH_PRE(false, 8);
+    else if (lanes == 16) FA2_LAUNCH_PRE(false, 16);
+    else FA2_LAUNCH_PRE(false, 32);
   }
+#undef FA2_LAUNCH_PRE
   return cudaGetLastError();
 }
 
