@@ -370,7 +370,7 @@ def run_ours(args, rank, world):
         tf = lambda fl, ms: fl / ms / 1e9  # noqa: E731
         traffic = None
         tfile = ROOT / "profiles" / "ncu_traffic.json"
-        if tfile.exists():
+        if tfile.exists() and (B, D) == (16, 128):
             traffic = json.loads(tfile.read_text()).get("bwd_kernel_dram_bytes_per_launch")
         cpu = None
         if world == 1 and not args.kernels_only:
@@ -383,11 +383,11 @@ def run_ours(args, rank, world):
                    "sample": f"{pairs} of the {B * H} (batch, head) units, forward + backward, fp32 on the host CPU"}
         achieved = tf(BWD_FLOPS, ms_bwd_kernel)
         line = {
-            "metric": METRIC if B == 16 else METRIC.replace("B16", f"B{B}") + " (reduced batch)",
+            "metric": METRIC if (B, D) == (16, 128) else METRIC.replace("B16", f"B{B}").replace("D128", f"D{D}") + " (not the headline configuration)",
             "value": tf(total, ms_step), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD if B == 16 else WORKLOAD.replace("B=16", f"B={B}") + " (reduced batch: not the headline configuration)",
+            "config": {"workload": WORKLOAD if (B, D) == (16, 128) else WORKLOAD.replace("B=16", f"B={B}").replace("D=128", f"D={D}") + " (not the headline configuration)",
                        "global_batch": B * world, "sharding": "independent batches per GPU",
                        "l2": "inputs and outputs (1.1 GB per step at B=16) exceed the 126 MB L2",
                        "value_path": "C ABI (fa2_fwd, fa2_bwd_preprocess, fa2_bwd) with a preallocated dQ accumulator, inputs resident in HBM",
@@ -402,9 +402,9 @@ def run_ours(args, rank, world):
                     frac_of_sustained_peak=None if not peak_sustained else tf(total / world, sustained["ms_per_step"]) / peak_sustained),
                 "long_context": long_context,
             },
-            "roofline": {"kernel": "bwd_kernel<128, bf16>", "bound": "tensor", "achieved": achieved, "peak": peak,
+            "roofline": {"kernel": "bwd_kernel<128, bf16>" if D <= 128 else "bwd_wide_kernel<bf16>", "bound": "tensor", "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind},
-            "roofline_fwd": {"kernel": "fwd_kernel<128, bf16>", "bound": "tensor", "achieved": tf(FWD_FLOPS, ms_fwd),
+            "roofline_fwd": {"kernel": "fwd_kernel<128, bf16>" if D <= 128 else "fwd_wide_kernel<bf16>", "bound": "tensor", "achieved": tf(FWD_FLOPS, ms_fwd),
                              "peak": peak, "unit": "TFLOP/s", "frac": tf(FWD_FLOPS, ms_fwd) / peak},
             "cpu_baseline": cpu,
             "e2e": None if ms_e2e is None else {"value": tf(total, ms_e2e), "unit": "TFLOP/s",
@@ -428,13 +428,17 @@ def main():
                     help="batch size; 16 is the benchmark, smaller values only size ncu captures")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (for ncu captures)")
+    ap.add_argument("--head-dim", type=int, default=128,
+                    help="head dim; 128 is the benchmark, others (with --kernels-only) size ncu captures of the other kernels")
     args = ap.parse_args()
+    if args.head_dim != 128 and not args.kernels_only:
+        ap.error("--head-dim other than 128 goes with --kernels-only")
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    global B, FWD_FLOPS, BWD_FLOPS
-    if args.batch != B:
-        B = args.batch
+    global B, D, FWD_FLOPS, BWD_FLOPS
+    if args.batch != B or args.head_dim != D:
+        B, D = args.batch, args.head_dim
         FWD_FLOPS = 4.0 * B * H * S * S * D * 0.5
         BWD_FLOPS = 2.5 * FWD_FLOPS
     if args.impl == "reference":
