@@ -87,3 +87,25 @@ def test_backward_formulas_with_softcap_and_alibi_match_autograd():
         torch.testing.assert_close(dq, qa.grad, atol=1e-5, rtol=1e-4)
         torch.testing.assert_close(dk, ka.grad, atol=1e-5, rtol=1e-4)
         torch.testing.assert_close(dv, va.grad, atol=1e-5, rtol=1e-4)
+
+
+def test_window_normalisation_follows_the_reference_host_layer():
+    """flash-attn2-rs/src/host/forward/mod.rs:310-320: sides of at least seqlen_k are open, causal sets right = 0,
+    ALiBi takes its key-position-only form when left is open and right is 0. Where the clamp changes the mask
+    (Sq > Sk, right window >= Sk) the rows before the first key see every key instead of none."""
+    from oracle.attention_oracle import attention_forward, normalise_windows
+
+    assert normalise_windows(False, 200, 130, 31) == (-1, -1, False)
+    assert normalise_windows(True, 300, -1, 256) == (-1, 0, True)
+    assert normalise_windows(False, 0, 5, 1) == (0, -1, False)
+    assert normalise_windows(False, -1, 0, 100) == (-1, 0, True)
+    assert normalise_windows(True, 64, 7, 100) == (64, 0, False)
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(1, 40, 2, 16, generator=g)
+    k = torch.randn(1, 8, 2, 16, generator=g)
+    v = torch.randn(1, 8, 2, 16, generator=g)
+    clamped = attention_forward(q, k, v, window_left=3, window_right=8)    # right >= Sk: open
+    open_right = attention_forward(q, k, v, window_left=3, window_right=-1)
+    assert torch.equal(clamped[0], open_right[0]) and torch.equal(clamped[1], open_right[1])
+    kept = attention_forward(q, k, v, window_left=3, window_right=7)       # right < Sk: rows 0..23 see no key
+    assert torch.isposinf(kept[1][:, :, :24]).all() and not torch.isposinf(kept[1][:, :, 25:]).any()
