@@ -114,3 +114,50 @@ def test_packed_random_case(seed):
     _close(dq, dq_ref, btol, "dq")
     _close(dk, dk_ref, btol, "dk")
     _close(dv, dv_ref, btol, "dv")
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_medium_random_case(seed):
+    """Enough (batch, head, query block) tiles that the persistent forward gives every CTA several of them with
+    different key ranges, and the backward several CTAs per SM; the oracle checks four sampled (batch, head)
+    units."""
+    from flash_attn2_b200 import cabi_ops as ops
+    from oracle.attention_oracle import attention_backward, attention_forward
+
+    r = random.Random(3000 + seed)
+    hk = r.choice([2, 4, 8])
+    group = r.choice([1, 2, 4])
+    h = hk * group
+    b = r.choice([2, 3, 4])
+    d = r.choice([64, 128, 128, 192, 256])
+    sq = r.choice([600, 777, 1024, 1300, 1700, 2048])
+    sk = r.choice([sq, sq, r.choice([640, 1111, 1536, 2200])])
+    dtype = r.choice([torch.float16, torch.bfloat16])
+    opt = r.choice([dict(causal=True), dict(causal=True), {}, dict(causal=True, window_left=r.choice([100, 300, 700])),
+                    dict(window_left=r.choice([50, 400]), window_right=r.choice([0, 64, 500]))])
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(b, sq, h, d, generator=g).to(dtype)
+    k = torch.randn(b, sk, hk, d, generator=g).to(dtype)
+    v = torch.randn(b, sk, hk, d, generator=g).to(dtype)
+    do = torch.randn(b, sq, h, d, generator=g).to(dtype)
+    qc, kc, vc, doc = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    out, lse = ops.fwd(qc, kc, vc, **opt)
+    delta = ops.bwd_preprocess(doc, out)
+    dq, dk, dv = ops.bwd(qc, kc, vc, doc, lse, delta, **opt)
+    assert ops.device_status() == 0
+    out, lse, dq, dk, dv = out.cpu(), lse.cpu(), dq.cpu(), dk.cpu(), dv.cpu()
+    ftol, btol = FWD_TOL[dtype], BWD_TOL[dtype]
+    for _ in range(4):
+        bi, kh = r.randrange(b), r.randrange(hk)
+        hs = slice(kh * group, (kh + 1) * group)  # the whole GQA group of one kv head: dK and dV sum over it
+        qs, ks, vs, dos = q[bi:bi + 1, :, hs], k[bi:bi + 1, :, kh:kh + 1], v[bi:bi + 1, :, kh:kh + 1], do[bi:bi + 1, :, hs]
+        o_ref, lse_ref = attention_forward(qs, ks, vs, **opt)
+        _close(out[bi:bi + 1, :, hs], o_ref, ftol, "out")
+        empty = torch.isposinf(lse_ref)
+        got_lse = lse[bi:bi + 1, hs]
+        assert (torch.isposinf(got_lse) == empty).all()
+        torch.testing.assert_close(got_lse[~empty], lse_ref[~empty], atol=ftol["lse"], rtol=0)
+        dq_ref, dk_ref, dv_ref, _ = attention_backward(qs, ks, vs, dos, out=out[bi:bi + 1, :, hs].float(), **opt)
+        _close(dq[bi:bi + 1, :, hs], dq_ref, btol, "dq")
+        _close(dk[bi:bi + 1, :, kh:kh + 1], dk_ref, btol, "dk")
+        _close(dv[bi:bi + 1, :, kh:kh + 1], dv_ref, btol, "dv")
