@@ -103,8 +103,11 @@ __global__ void __launch_bounds__(256) preprocess_kernel(const PreprocessParams 
 template <bool BF16>
 __global__ void __launch_bounds__(256) dq_convert_kernel(const float4* __restrict__ src, uint4* __restrict__ dst,
                                                          int64_t n8, float scale) {
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n8;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+  // From the end of the accumulator to its start: the backward kernel walks the heads in ascending order, so
+  // what it touched last (and the L2 still holds) sits at the end.
+  for (int64_t j = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; j < n8;
+       j += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t i = n8 - 1 - j;
     const float4 a = src[2 * i], b = src[2 * i + 1];
     uint4 w;
     if constexpr (BF16) {
