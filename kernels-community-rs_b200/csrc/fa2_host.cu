@@ -440,7 +440,8 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
     p.tm_dv = p.tm_v;
   }
   if (want_dq) {
-    if ((rc = make_map(&p.tm_dqa, a->dq_accum, 2, 4, d, a->heads, rows_q, nbatch, d, hd, rows_q * hd, 32, 32,
+    // one reduce-add box: 32 columns of 32 query rows (64 on the kernel for head dims above 128)
+    if ((rc = make_map(&p.tm_dqa, a->dq_accum, 2, 4, d, a->heads, rows_q, nbatch, d, hd, rows_q * hd, 32, wide ? 64 : 32,
                        "dq_accum")) != FA2_OK) return rc;
   } else {
     p.tm_dqa = p.tm_q;
@@ -500,6 +501,10 @@ int bwd_impl(const fa2_bwd_args* a, void* stream_v) {
   p.head_dim = d;
   p.dq_acc = static_cast<float*>(a->dq_accum);
   p.dq_rows = rows_q;
+  p.v_ptr = a->v;
+  p.v_batch_stride = packed ? 0 : a->v_stride[0];
+  p.v_row_stride = a->v_stride[1];
+  p.v_head_stride = a->v_stride[2];
   e = wide ? fa2::launch_bwd_wide(p, d, a->dtype == FA2_BF16, stream)
            : fa2::launch_bwd(p, d, a->dtype == FA2_BF16, rt->sm_count, stream);
   if (a->ev_kernel_stop != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->ev_kernel_stop), stream);

@@ -81,6 +81,9 @@ struct BwdParams {
   // dq_acc[((batch * dq_rows + row) * heads + head) * head_dim + d], dq_rows rows per batch entry.
   float* dq_acc;
   int64_t dq_rows;
+  // That kernel reads V row by row from global memory (it keeps V in TMEM): element strides of [batch, row, head].
+  const void* v_ptr;
+  int64_t v_batch_stride, v_row_stride, v_head_stride;
 };
 
 struct PreprocessParams {

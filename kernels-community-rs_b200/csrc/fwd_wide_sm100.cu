@@ -120,7 +120,10 @@ __device__ __forceinline__ float wide_tanh(float x) {
   return y;
 }
 
-template <bool BF16>
+// ATOMS: 64-column atoms of the head dim that are loaded (3 for head dims up to 192, else 4). TMA fills what lies
+// past the real head dim inside them with zeros, so Q K^T runs over ATOMS * 64 columns with compile-time operand
+// offsets: a runtime bound in the issuing thread's loop doubles the cost of an MMA issue.
+template <bool BF16, int ATOMS>
 __global__ void __launch_bounds__(kWThreads, 1) fwd_wide_kernel(const __grid_constant__ FwdParams p) {
   using Cfg = WideCfg;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -150,8 +153,8 @@ __global__ void __launch_bounds__(kWThreads, 1) fwd_wide_kernel(const __grid_con
   const WaitCtl ctl{abort_flag, p.status};
   const WTile ti = get_wtile(p, blockIdx.x);
   if (!ti.valid) return;
-  const int atoms = (p.head_dim + 63) / 64;  // 64-column atoms that hold real columns (3 or 4)
-  const int n_cols = atoms * 64;             // columns of O in TMEM
+  constexpr int atoms = ATOMS;
+  constexpr int n_cols = atoms * 64;         // columns of O in TMEM
   const int n_tiles = ti.ne - ti.nb;
 
   if (n_tiles == 0) {
@@ -427,7 +430,7 @@ __global__ void __launch_bounds__(kWThreads, 1) fwd_wide_kernel(const __grid_con
     const uint64_t k_desc = make_smem_desc(smem_u32(s_kv), 16, 1024);              // K-major B
     const uint64_t v_desc = make_smem_desc(smem_u32(s_kv), Cfg::kAtomKV, 1024);    // MN-major B
     const uint64_t p_desc = make_smem_desc(smem_u32(s_p), 16, 1024);               // K-major A
-    const int n_ks = (p.head_dim + 15) / 16;  // steps of 16 over the head dim; what TMA left past it is zero
+    constexpr int n_ks = ATOMS * 4;  // steps of 16 over the loaded columns
     const uint32_t t_s = tmem + Cfg::kTmemS;
     const uint32_t t_o = tmem + Cfg::kTmemO;
     uint32_t slot = 0, ring_phase = 0;
@@ -451,11 +454,10 @@ __global__ void __launch_bounds__(kWThreads, 1) fwd_wide_kernel(const __grid_con
       // Compile-time operand offsets: a rolled loop that builds descriptors costs the issuing thread about twice
       // the 54 cycles such an MMA takes.
       const uint32_t d_s = t_s + buf * kWN;
-      static_for<16>([&](auto ks) {
+      static_for<n_ks>([&](auto ks) {
         constexpr uint32_t in_atom = (ks.value & 3) * 2;
-        if (ks.value < n_ks)
-          mma_ss_o<(ks.value >> 2) * kAtomQ16 + in_atom, (ks.value >> 2) * kAtomKV16 + in_atom>(d_s, q_desc, b, idesc_qk,
-                                                                                             ks.value > 0 ? 1u : 0u);
+        mma_ss_o<(ks.value >> 2) * kAtomQ16 + in_atom, (ks.value >> 2) * kAtomKV16 + in_atom>(d_s, q_desc, b, idesc_qk,
+                                                                                           ks.value > 0 ? 1u : 0u);
       });
       mma_commit(&s_full[buf]);
       advance();
@@ -498,20 +500,20 @@ __global__ void __launch_bounds__(kWThreads, 1) fwd_wide_kernel(const __grid_con
   if (warp == kWMmaWarp) tmem_dealloc(tmem, 512);
 }
 
-template <bool BF16>
+template <bool BF16, int ATOMS>
 cudaError_t launch_wide(const FwdParams& p, cudaStream_t stream) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(fwd_wide_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, WideCfg::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(fwd_wide_kernel<BF16, ATOMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, WideCfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
   const int64_t blocks = static_cast<int64_t>((p.seqlen_q + kWM - 1) / kWM) * p.batch * p.heads;
   if (blocks <= 0) return cudaSuccess;
   if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
-  fwd_wide_kernel<BF16><<<static_cast<unsigned>(blocks), kWThreads, WideCfg::kSmemBytes, stream>>>(p);
+  fwd_wide_kernel<BF16, ATOMS><<<static_cast<unsigned>(blocks), kWThreads, WideCfg::kSmemBytes, stream>>>(p);
   return cudaGetLastError();
 }
 
@@ -519,7 +521,8 @@ cudaError_t launch_wide(const FwdParams& p, cudaStream_t stream) {
 
 cudaError_t launch_fwd_wide(const FwdParams& p, int head_dim, bool bf16, cudaStream_t stream) {
   if (head_dim <= 128 || head_dim > 256 || head_dim % 8 != 0) return cudaErrorInvalidValue;
-  return bf16 ? launch_wide<true>(p, stream) : launch_wide<false>(p, stream);
+  if (head_dim <= 192) return bf16 ? launch_wide<true, 3>(p, stream) : launch_wide<false, 3>(p, stream);
+  return bf16 ? launch_wide<true, 4>(p, stream) : launch_wide<false, 4>(p, stream);
 }
 
 }  // namespace fa2
