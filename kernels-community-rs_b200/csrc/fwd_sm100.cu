@@ -78,7 +78,7 @@ struct FwdCfg {
   static constexpr int kBarOff = kOOff + 2 * kStageBufBytes;
   static constexpr int kNumBars = 3 * kSlots + 18 + 2 * kPQ;  // kv_full, kv_empty, kv_fixed + per stage
   static constexpr int kMiscOff = (kBarOff + kNumBars * 8 + 15) / 16 * 16;  // tmem slot, abort flag
-  static constexpr int kSmemBytes = kMiscOff + 32;  // the dynamic window must start 1024-aligned
+  static constexpr int kSmemBytes = kMiscOff + 48;  // tmem slot, abort flag, ListDiv; the dynamic window must start 1024-aligned
   static constexpr uint32_t kTmemS0 = 0, kTmemS1 = 128, kTmemO0 = 256, kTmemO1 = 256 + D;
 };
 
@@ -94,52 +94,45 @@ struct Tile {
   bool valid;
 };
 
-// Divisors of the work-list index, with their float reciprocals: an integer division is a long dependent
-// chain, every role walks the list, and the softmax warps do so between two tiles while the other stage's warp
-// keeps the scheduler busy. n / d for 0 <= n < 2^24 is the float estimate walked to the exact quotient.
-// The four reciprocals live in shared memory (written once by thread 0), not in registers.
+// Divisors of the work-list index as fixed-point reciprocals floor(2^40 / d) + 1: an integer division is a long
+// dependent chain, every role walks the list, and the softmax warps do so between two tiles. The quotient is one
+// 64-bit multiply, a shift and a correction on the integer pipes; going through float reciprocals instead put
+// int <-> float conversions on the MUFU unit, behind the other stage's exponentials (1000-3500 cycles a tile).
+// n / d for 0 <= n < 2^24; the four constants live in shared memory (written once by thread 0).
 struct ListDiv {
-  float inv_grid, inv_bh, inv_heads, inv_group;
+  unsigned long long grid, bh, heads, group;
 };
 __device__ __forceinline__ void make_list_div(const FwdParams& p, volatile ListDiv* d) {
-  d->inv_grid = __frcp_rn(__int2float_rn(static_cast<int>(gridDim.x)));
-  d->inv_bh = __frcp_rn(__int2float_rn(p.batch * p.heads));
-  d->inv_heads = __frcp_rn(__int2float_rn(p.heads));
-  d->inv_group = __frcp_rn(__int2float_rn(p.group));
+  d->grid = (1ull << 40) / gridDim.x + 1;
+  d->bh = (1ull << 40) / static_cast<unsigned>(p.batch * p.heads) + 1;
+  d->heads = (1ull << 40) / static_cast<unsigned>(p.heads) + 1;
+  d->group = (1ull << 40) / static_cast<unsigned>(p.group) + 1;
 }
-__device__ __forceinline__ int div_small(int n, int d, float inv) {
+__device__ __forceinline__ int div_small(int n, int d, unsigned long long m) {
   if (n >= (1 << 24)) return n / d;
-  int q = __float2int_rz(__int2float_rz(n) * inv);
-  int r = n - q * d;
-  while (r >= d) {
-    ++q;
-    r -= d;
-  }
-  while (r < 0) {
-    --q;
-    r += d;
-  }
+  int q = static_cast<int>((static_cast<unsigned long long>(static_cast<unsigned>(n)) * m) >> 40);
+  if (q * d > n) --q;  // the reciprocal is rounded up: the estimate can be one too large for d >= 2^16
   return q;
 }
 
 __device__ __forceinline__ Tile get_tile(const FwdParams& p, const volatile ListDiv* ldp, int t) {
-  const ListDiv ld{ldp->inv_grid, ldp->inv_bh, ldp->inv_heads, ldp->inv_group};
+  const ListDiv ld{ldp->grid, ldp->bh, ldp->heads, ldp->group};
   Tile ti;
   // Work tiles are listed longest first; CTA c takes list entries c, 2G-1-c, 2G+c, 4G-1-c, ... (G CTAs):
   // reversing every other round evens out the work per CTA when the sizes fall off in plateaus.
   const int grid = static_cast<int>(gridDim.x);
-  const int round = div_small(t, grid, ld.inv_grid);
+  const int round = div_small(t, grid, ld.grid);
   const int pos = (round & 1) ? round * grid + (grid - 1 - (t - round * grid)) : t;
   if (pos >= p.num_tiles) {
     ti.valid = false;
     return ti;
   }
   const int bh = p.batch * p.heads;
-  const int mrev = div_small(pos, bh, ld.inv_bh);
+  const int mrev = div_small(pos, bh, ld.bh);
   const int rem = pos - mrev * bh;
-  ti.b = div_small(rem, p.heads, ld.inv_heads);
+  ti.b = div_small(rem, p.heads, ld.heads);
   ti.h = rem - ti.b * p.heads;
-  ti.hk = div_small(ti.h, p.group, ld.inv_group);
+  ti.hk = div_small(ti.h, p.group, ld.group);
   ti.m0 = (p.num_mblk - 1 - mrev) * (2 * kBlockM);
   if (p.cu_q != nullptr) {
     ti.q_row0 = p.cu_q[ti.b];
