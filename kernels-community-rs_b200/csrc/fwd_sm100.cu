@@ -91,6 +91,7 @@ struct Tile {
   int off;             // sk - sq (bottom-right alignment)
   int nb[2], ne[2];    // key-tile range per stage; nb == ne means no work
   int jlo, jhi;
+  int flip;            // 1: stage 0 takes the upper 128 rows of the block and stage 1 the lower ones
   bool valid;
 };
 
@@ -123,6 +124,10 @@ __device__ __forceinline__ Tile get_tile(const FwdParams& p, const volatile List
   const int grid = static_cast<int>(gridDim.x);
   const int round = div_small(t, grid, ld.grid);
   const int pos = (round & 1) ? round * grid + (grid - 1 - (t - round * grid)) : t;
+  // Under a causal mask the upper half of a block sees one key tile more than the lower one. The stages run
+  // independently through the CTA's list, so they take the halves in turns: otherwise stage 1 would end up with
+  // about 6 % more key tiles than stage 0 at S = 2048 and the CTA would wait for it.
+  ti.flip = round & 1;
   if (pos >= p.num_tiles) {
     ti.valid = false;
     return ti;
@@ -155,7 +160,7 @@ __device__ __forceinline__ Tile get_tile(const FwdParams& p, const volatile List
   ti.jhi = 0;
 #pragma unroll
   for (int s = 0; s < 2; ++s) {
-    const int r_lo = ti.m0 + s * kBlockM;
+    const int r_lo = ti.m0 + (s ^ ti.flip) * kBlockM;
     int nb = 0, ne = 0;
     if (r_lo < ti.sq) {
       const int r_hi = min(r_lo + kBlockM - 1, ti.sq - 1);
@@ -285,7 +290,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
     for (int t = blockIdx.x; t - static_cast<int>(blockIdx.x) < p.num_tiles; t += gridDim.x) {
       const Tile ti = get_tile(p, ld, t);
       if (!ti.valid) continue;
-      const int r_lo = ti.m0 + s * kBlockM;
+      const int r_lo = ti.m0 + (s ^ ti.flip) * kBlockM;
       const int row = r_lo + row_in;
       const int nb_s = s ? ti.nb[1] : ti.nb[0];
       const int ne_s = s ? ti.ne[1] : ti.ne[0];
@@ -598,7 +603,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
 #pragma unroll
           for (int a = 0; a < Cfg::kAtoms; ++a)
             tma_load_4d(s_q + s * Cfg::kTileBytes + a * (kBlockM * 128), &p.tm_q, &q_full[s], a * 64, ti.h,
-                        ti.q_row0 + ti.m0 + s * kBlockM, ti.bq);
+                        ti.q_row0 + ti.m0 + (s ^ ti.flip) * kBlockM, ti.bq);
           return true;
         };
         // Ring order K(jlo), K(jlo+1), V(jlo), K(jlo+2), V(jlo+1), ...: Q K^T runs one key tile ahead of P V.
