@@ -130,7 +130,10 @@ __device__ __forceinline__ KvTile get_kv_tile(const BwdParams& p, int t) {
   return ti;
 }
 
-template <int D, bool BF16>
+// FANCY: softcap or ALiBi in use; PACKED: cu_seqlens batches. Both are compile-time so that the plain dense
+// kernel carries none of their code: at 156 KB the all-in-one kernel missed the SM's instruction cache on a
+// quarter of its fetches and ran 6-9 % slower than the 62 KB one.
+template <int D, bool BF16, bool FANCY, bool PACKED>
 __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant__ BwdParams p) {
   using Cfg = BwdCfg<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -243,7 +246,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
 
   if (warp < 4) {
     reg_dealloc<kMiscRegs>();
-    if (warp == 0 && lane == 0) {
+    if (warp == 0 && elect_one()) {
       // ---------------------------------------------------------------- loader
       // K, V and the first Q / dO tiles were requested during set-up.
       bool ok = true;
@@ -274,7 +277,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         while (clock64() - t0 < 2000000) {
         }
       }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1 && elect_one()) {
       // ---------------------------------------------------------------- mma issuer
       // Descriptors are built once; in the loops an operand address is one 64-bit add of a constant
       // (the descriptor's address field counts 16-byte units).
@@ -303,7 +306,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       };
       // Packed batches: a tile that reaches past the end of its sequence holds rows of the next sequence; it
       // is usable once the fixer warp has cleared them. bit st of *_par: parity of the stage's next fix.
-      const bool packed = p.cu_q != nullptr;
+      constexpr bool packed = PACKED;
       uint32_t qfix_par = 0, dofix_par = 0;
       auto ragged_q = [&](int mi) { return packed && (ti.m_start + mi) * kBlk + kBlk > ti.sq; };
       auto q_ready = [&](int mi, uint32_t st, uint32_t ph, int code) -> bool {
@@ -392,7 +395,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         }
       }
       if (ok) mma_commit(dkv_done);
-    } else if (warp == 2 && p.cu_q != nullptr && n_iter > 0) {
+    } else if (PACKED && warp == 2 && n_iter > 0) {
       // ---------------------------------------------------------------- fixer (packed batches)
       // The reference zero-fills the rows of a tile that lie past the end of the sequence while staging it
       // (flash-attn2-rs/src/device/varlen/backward.rs:134-648 through the zfill copies of
@@ -466,7 +469,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         v = p.delta[ti.bq * p.delta_batch_stride + hq * p.delta_head_stride + ti.q_row0 + ti.b * p.delta_seq_pad + q];
       return v;
     };
-    const bool fancy = (p.softcap > 0.f) || (p.alibi != nullptr);
+    constexpr bool fancy = FANCY;
     Walk w{0, 0};
     float stat_next = n_iter > 0 ? load_stat(w) : 0.f;
     for (int it = 0; it < n_iter; ++it) {
@@ -584,7 +587,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       const CUtensorMap* tm = (wg == 0) ? &p.tm_dk : &p.tm_dv;
       uint16_t* gptr = reinterpret_cast<uint16_t*>(wg == 0 ? p.dk_ptr : p.dv_ptr);
       const bool store = (p.which & 2) != 0;
-      const bool tma_store = (p.cu_k == nullptr) || (ti.n0 + kBlk <= ti.sk);
+      const bool tma_store = !PACKED || (ti.n0 + kBlk <= ti.sk);
       // Staging tile of the bulk store: the K tile for dK, the V tile for dV (their last readers have completed
       // with dkv_done; the Q and dO stages may still hold dQ pieces of the last iteration's drain).
       uint8_t* stage = (wg == 0) ? s_k : s_v;
@@ -655,7 +658,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         // Packed batches: the 32-row boxes of the reduce-adds below reach past the end of the sequence into
         // the next sequence's rows. Rows past the end hold nothing of this sequence (and possibly NaN, when this
         // sequence's own data is not finite): they add exact zeros.
-        if (p.cu_q != nullptr && m0 + (warp & 3) * 32 + lane >= ti.sq) {
+        if (PACKED && m0 + (warp & 3) * 32 + lane >= ti.sq) {
 #pragma unroll
           for (int i = 0; i < D; ++i) acc[i] = 0u;
         }
@@ -758,7 +761,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool FANCY, bool PACKED>
 cudaError_t launch_one(const BwdParams& p, int num_ctas, cudaStream_t stream) {
   using Cfg = BwdCfg<D>;
   static bool configured[64] = {};
@@ -766,12 +769,29 @@ cudaError_t launch_one(const BwdParams& p, int num_ctas, cudaStream_t stream) {
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
     cudaError_t e =
-        cudaFuncSetAttribute(bwd_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        cudaFuncSetAttribute(bwd_kernel<D, BF16, FANCY, PACKED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  bwd_kernel<D, BF16><<<num_ctas, kThreads, Cfg::kSmemBytes, stream>>>(p);
+  bwd_kernel<D, BF16, FANCY, PACKED><<<num_ctas, kThreads, Cfg::kSmemBytes, stream>>>(p);
   return cudaGetLastError();
+}
+
+template <int D, bool BF16>
+cudaError_t pick_features(const BwdParams& p, bool fancy, bool packed, int num_ctas, cudaStream_t stream) {
+  if (fancy) {
+    return packed ? launch_one<D, BF16, true, true>(p, num_ctas, stream)
+                  : launch_one<D, BF16, true, false>(p, num_ctas, stream);
+  }
+  return packed ? launch_one<D, BF16, false, true>(p, num_ctas, stream)
+                : launch_one<D, BF16, false, false>(p, num_ctas, stream);
+}
+
+template <int D>
+cudaError_t pick_dtype(const BwdParams& p, bool bf16, bool fancy, bool packed, int num_ctas, cudaStream_t stream) {
+  return bf16 ? pick_features<D, true>(p, fancy, packed, num_ctas, stream)
+              : pick_features<D, false>(p, fancy, packed, num_ctas, stream);
 }
 
 }  // namespace
@@ -779,9 +799,11 @@ cudaError_t launch_one(const BwdParams& p, int num_ctas, cudaStream_t stream) {
 cudaError_t launch_bwd(const BwdParams& p, int head_dim, bool bf16, int /*num_sms*/, cudaStream_t stream) {
   const int num_ctas = p.num_nblk * p.batch * p.heads_k;
   if (num_ctas <= 0) return cudaSuccess;
-  if (head_dim > 64 && head_dim <= 128) return bf16 ? launch_one<128, true>(p, num_ctas, stream) : launch_one<128, false>(p, num_ctas, stream);
-  if (head_dim > 0 && head_dim <= 64) return bf16 ? launch_one<64, true>(p, num_ctas, stream) : launch_one<64, false>(p, num_ctas, stream);
-  return cudaErrorInvalidValue;
+  if (head_dim <= 0 || head_dim > 128) return cudaErrorInvalidValue;
+  const bool fancy = (p.softcap > 0.f) || (p.alibi != nullptr);
+  const bool packed = p.cu_q != nullptr;
+  return head_dim > 64 ? pick_dtype<128>(p, bf16, fancy, packed, num_ctas, stream)
+                       : pick_dtype<64>(p, bf16, fancy, packed, num_ctas, stream);
 }
 
 }  // namespace fa2

@@ -231,6 +231,15 @@ __device__ __forceinline__ void mma_ts_o(uint32_t d_tmem, uint32_t a_tmem, uint6
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "n"(ACOL), "n"(BOFF16)
       : "memory");
 }
+// True in exactly one lane of a converged warp. A single-thread role entered through this predicate, rather than
+// through a comparison of the lane index, lets the compiler keep the role's descriptors, addresses and loop
+// counters in uniform registers: the issuer loop of the backward kernel shrank from 14.5 KB to 6.7 KB of code.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
 // Calls f(std::integral_constant<int, 0>{}) ... f(integral_constant<int, N-1>{}).
 template <int N, int I = 0, class F>
 __device__ __forceinline__ void static_for(F&& f) {
