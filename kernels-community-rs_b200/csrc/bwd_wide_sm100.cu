@@ -126,7 +126,9 @@ __device__ __forceinline__ WKvTile get_wkv_tile(const BwdParams& p, int t) {
 // ATOMS: 64-column atoms of the head dim that are loaded (3 for head dims up to 192, else 4). TMA fills what lies
 // past the real head dim inside them with zeros, so every contraction runs over ATOMS * 64 columns with
 // compile-time operand offsets: a runtime bound in the issuing thread's loops doubles the cost of an MMA issue.
-template <bool BF16, int ATOMS>
+// FANCY (softcap or ALiBi in use) and PACKED (cu_seqlens batches) are compile-time: the plain dense kernel carries
+// none of their code, which keeps its loops within reach of the SM's instruction cache.
+template <bool BF16, int ATOMS, bool FANCY, bool PACKED>
 __global__ void __launch_bounds__(kBWThreads, 1) bwd_wide_kernel(const __grid_constant__ BwdParams p) {
   using Cfg = BwdWideCfg;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -170,7 +172,7 @@ __global__ void __launch_bounds__(kBWThreads, 1) bwd_wide_kernel(const __grid_co
   const int ncol = min(128, atoms * 64 - ti.half * 128);     // columns of this CTA's half (128 or 64)
   const int n_iter = ti.n_iter;
   const bool want_dq = (p.which & 1) != 0;
-  const bool packed = p.cu_q != nullptr;
+  constexpr bool packed = PACKED;
 
   if (tid == 0) {
     *abort_flag = 0;
@@ -261,7 +263,7 @@ __global__ void __launch_bounds__(kBWThreads, 1) bwd_wide_kernel(const __grid_co
     };
     const float inv_cap = (p.softcap > 0.f) ? p.scale / p.softcap : 0.f;
     const float cap_l2 = p.softcap * kBWLog2e;
-    const bool fancy = (p.softcap > 0.f) || (p.alibi != nullptr);
+    constexpr bool fancy = FANCY;
     WWalk w{0, 0};
     float stat_next = n_iter > 0 ? load_stat(w) : 0.f;
     for (int it = 0; it < n_iter; ++it) {
@@ -442,7 +444,7 @@ __global__ void __launch_bounds__(kBWThreads, 1) bwd_wide_kernel(const __grid_co
     }
     __syncwarp();
   } else if (warp == kBWLoadWarp) {
-    if (lane == 0 && n_iter > 0) {
+    if (n_iter > 0 && elect_one()) {
       // ---------------------------------------------------------------- loader
       mbar_expect_tx(k_full, atoms * Cfg::kAtomK);
       for (int a = 0; a < atoms; ++a) tma_load_4d(s_k + a * Cfg::kAtomK, &p.tm_k, k_full, a * 64, ti.hk, ti.k_row0 + ti.n0, ti.bq);
@@ -518,7 +520,7 @@ __global__ void __launch_bounds__(kBWThreads, 1) bwd_wide_kernel(const __grid_co
         }
       }
     }
-  } else if (warp == kBWMmaWarp && lane == 0 && n_iter > 0) {
+  } else if (warp == kBWMmaWarp && n_iter > 0 && elect_one()) {
     // ---------------------------------------------------------------- mma issuer
     const uint32_t fmt = BF16 ? 1u : 0u;
     const uint32_t kBase = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(kBK >> 4) << 24);
@@ -657,30 +659,43 @@ __global__ void __launch_bounds__(kBWThreads, 1) bwd_wide_kernel(const __grid_co
   if (warp == kBWMmaWarp) tmem_dealloc(tmem, 512);
 }
 
-template <bool BF16, int ATOMS>
+template <bool BF16, int ATOMS, bool FANCY, bool PACKED>
 cudaError_t launch_bwd_wide_one(const BwdParams& p, cudaStream_t stream) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(bwd_wide_kernel<BF16, ATOMS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         BwdWideCfg::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(bwd_wide_kernel<BF16, ATOMS, FANCY, PACKED>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, BwdWideCfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
   const int64_t blocks = 2LL * p.num_nblk * p.batch * p.heads_k;
   if (blocks <= 0) return cudaSuccess;
   if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
-  bwd_wide_kernel<BF16, ATOMS><<<static_cast<unsigned>(blocks), kBWThreads, BwdWideCfg::kSmemBytes, stream>>>(p);
+  bwd_wide_kernel<BF16, ATOMS, FANCY, PACKED>
+      <<<static_cast<unsigned>(blocks), kBWThreads, BwdWideCfg::kSmemBytes, stream>>>(p);
   return cudaGetLastError();
+}
+
+template <bool BF16, int ATOMS>
+cudaError_t pick_features(const BwdParams& p, cudaStream_t stream) {
+  const bool fancy = (p.softcap > 0.f) || (p.alibi != nullptr);
+  const bool packed = p.cu_q != nullptr;
+  if (fancy) {
+    return packed ? launch_bwd_wide_one<BF16, ATOMS, true, true>(p, stream)
+                  : launch_bwd_wide_one<BF16, ATOMS, true, false>(p, stream);
+  }
+  return packed ? launch_bwd_wide_one<BF16, ATOMS, false, true>(p, stream)
+                : launch_bwd_wide_one<BF16, ATOMS, false, false>(p, stream);
 }
 
 }  // namespace
 
 cudaError_t launch_bwd_wide(const BwdParams& p, int head_dim, bool bf16, cudaStream_t stream) {
   if (head_dim <= 128 || head_dim > 256 || head_dim % 8 != 0) return cudaErrorInvalidValue;
-  if (head_dim <= 192) return bf16 ? launch_bwd_wide_one<true, 3>(p, stream) : launch_bwd_wide_one<false, 3>(p, stream);
-  return bf16 ? launch_bwd_wide_one<true, 4>(p, stream) : launch_bwd_wide_one<false, 4>(p, stream);
+  if (head_dim <= 192) return bf16 ? pick_features<true, 3>(p, stream) : pick_features<false, 3>(p, stream);
+  return bf16 ? pick_features<true, 4>(p, stream) : pick_features<false, 4>(p, stream);
 }
 
 }  // namespace fa2

@@ -186,8 +186,9 @@ __device__ __forceinline__ Tile get_tile(const FwdParams& p, const volatile List
 
 // First row of key tile j that lies past the end of a packed sequence (kBlockN = none). Dense tensors need
 // nothing: the TMA unit fills rows past the tensor with zeros.
-__device__ __forceinline__ int ragged_row(const FwdParams& p, int sk, int j) {
-  if (p.cu_q == nullptr) return kBlockN;
+template <bool PACKED>
+__device__ __forceinline__ int ragged_row(int sk, int j) {
+  if (!PACKED) return kBlockN;
   const int left = sk - j * kBlockN;
   return left < kBlockN ? max(left, 0) : kBlockN;
 }
@@ -198,7 +199,10 @@ __device__ __forceinline__ float tanh_approx(float x) {
   return y;
 }
 
-template <int D, bool BF16>
+// FANCY: softcap, ALiBi or a negative scale in use; PACKED: cu_seqlens batches. Both are compile-time so that the
+// plain dense kernel carries none of their code and stays within reach of the SM's instruction cache: without the
+// score transforms the kernel is a third smaller and ran 3-4 % faster.
+template <int D, bool BF16, bool FANCY, bool PACKED>
 __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
   using Cfg = FwdCfg<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -285,7 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
       const uint32_t addr = p_row + (c >> 3) * (kBlockM * 128) + ((static_cast<uint32_t>(c & 7) << 4) ^ p_swz);
       asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
     };
-    const bool fancy = (p.softcap > 0.f) || (p.alibi != nullptr) || (p.scale_log2 < 0.f);
+    constexpr bool fancy = FANCY;
     uint32_t n_sfull = 0, n_pv = 0, n_store = 0, n_first = 0;
     for (int t = blockIdx.x; t - static_cast<int>(blockIdx.x) < p.num_tiles; t += gridDim.x) {
       const Tile ti = get_tile(p, ld, t);
@@ -502,7 +506,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
       // A ragged tile of a packed batch (rows of the next sequence follow) uses predicated stores.
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.o_ptr) + ti.bq * p.o_batch_stride +
                        static_cast<int64_t>(ti.q_row0 + row) * p.o_row_stride + ti.h * p.o_head_stride;
-      const bool tma_store = (p.cu_q == nullptr) || (r_lo + kBlockM <= ti.sq);
+      const bool tma_store = !PACKED || (r_lo + kBlockM <= ti.sq);
       if (ne_s > nb_s) {
         const float inv_l = (l > 0.f) ? 1.f / l : 0.f;  // before the wait: the reciprocal queues behind the other stage's exp2 stream
         if (!warp_wait(&pv_done[s], (n_pv - 1) & 1, ctl, kWaitEpiPvDone)) break;
@@ -574,7 +578,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
     __syncwarp();
   } else {
     reg_dealloc<kOtherRegs>();
-    if (warp == kLoadWarp && lane == 0) {
+    if (warp == kLoadWarp && elect_one()) {
       // ---------------------------------------------------------------- loader
       uint32_t slot = 0, ring_phase = 0, n_q0 = 0, n_q1 = 0;
       bool ok = true;
@@ -631,7 +635,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
       // ---------------------------------------------------------------- fixer (packed batches)
       // Walks the ring in the loader's order and waits for every tile, which keeps it within one ring
       // pass of the consumers; it acts on V tiles that reach past the end of their sequence.
-      if (p.cu_q != nullptr) {
+      if (PACKED) {
         uint32_t slot = 0, ring_phase = 0;
         bool ok = true;
         auto step = [&](int first_stray) -> bool {
@@ -660,11 +664,11 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           if (ti.jlo < ti.jhi) ok = step(kBlockN);
           for (int j = ti.jlo; j < ti.jhi && ok; ++j) {
             if (j + 1 < ti.jhi) ok = step(kBlockN);
-            if (ok) ok = step(ragged_row(p, ti.sk, j));
+            if (ok) ok = step(ragged_row<PACKED>(ti.sk, j));
           }
         }
       }
-    } else if ((warp == kMmaWarp || warp == kMmaWarp1) && lane == 0) {
+    } else if ((warp == kMmaWarp || warp == kMmaWarp1) && elect_one()) {
       // ---------------------------------------------------------------- mma issuer
       // Descriptors are built once; inside the loops an operand address is one 64-bit add of a
       // compile-time constant (descriptor address field is in 16-byte units), so that the single
@@ -732,7 +736,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         // P row inside its swizzle atom, 16 rows of 128 bytes of V).
         auto do_v = [&](const int j) -> bool {
           if (!mbar_wait(&kv_full[slot], ring_phase, ctl, kWaitMmaKVFull)) return false;
-          if (ragged_row(p, ti.sk, j) < kBlockN) {
+          if (ragged_row<PACKED>(ti.sk, j) < kBlockN) {
             // A V tile that reaches past its sequence is usable once the fixer has cleared the stray rows.
             if (!mbar_wait(&kv_fixed[slot], (fix_par >> slot) & 1, ctl, kWaitMmaKVFull)) return false;
             fix_par ^= 1u << slot;
@@ -781,7 +785,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   if (warp == kMmaWarp) tmem_dealloc(tmem, 512);
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool FANCY, bool PACKED>
 cudaError_t launch_one(const FwdParams& p, int num_sms, cudaStream_t stream) {
   using Cfg = FwdCfg<D>;
   static bool configured[64] = {};
@@ -789,24 +793,42 @@ cudaError_t launch_one(const FwdParams& p, int num_sms, cudaStream_t stream) {
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
     cudaError_t e =
-        cudaFuncSetAttribute(fwd_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        cudaFuncSetAttribute(fwd_kernel<D, BF16, FANCY, PACKED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
   const int grid = p.num_tiles < num_sms ? p.num_tiles : num_sms;
-  fwd_kernel<D, BF16><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(p);
+  fwd_kernel<D, BF16, FANCY, PACKED><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(p);
   return cudaGetLastError();
+}
+
+template <int D, bool BF16>
+cudaError_t pick_features(const FwdParams& p, bool fancy, bool packed, int num_sms, cudaStream_t stream) {
+  if (fancy) {
+    return packed ? launch_one<D, BF16, true, true>(p, num_sms, stream)
+                  : launch_one<D, BF16, true, false>(p, num_sms, stream);
+  }
+  return packed ? launch_one<D, BF16, false, true>(p, num_sms, stream)
+                : launch_one<D, BF16, false, false>(p, num_sms, stream);
+}
+
+template <int D>
+cudaError_t pick_dtype(const FwdParams& p, bool bf16, bool fancy, bool packed, int num_sms, cudaStream_t stream) {
+  return bf16 ? pick_features<D, true>(p, fancy, packed, num_sms, stream)
+              : pick_features<D, false>(p, fancy, packed, num_sms, stream);
 }
 
 }  // namespace
 
-
 cudaError_t launch_fwd(const FwdParams& p, int head_dim, bool bf16, int num_sms, cudaStream_t stream) {
   if (p.num_tiles <= 0) return cudaSuccess;
   // Head dims below the kernel's D ride on TMA: loads past the real head dim read zeros, stores are clipped.
-  if (head_dim > 64 && head_dim <= 128) return bf16 ? launch_one<128, true>(p, num_sms, stream) : launch_one<128, false>(p, num_sms, stream);
-  if (head_dim > 0 && head_dim <= 64) return bf16 ? launch_one<64, true>(p, num_sms, stream) : launch_one<64, false>(p, num_sms, stream);
-  return cudaErrorInvalidValue;
+  if (head_dim <= 0 || head_dim > 128) return cudaErrorInvalidValue;
+  const bool fancy = (p.softcap > 0.f) || (p.alibi != nullptr) || (p.scale_log2 < 0.f);
+  const bool packed = p.cu_q != nullptr;
+  return head_dim > 64 ? pick_dtype<128>(p, bf16, fancy, packed, num_sms, stream)
+                       : pick_dtype<64>(p, bf16, fancy, packed, num_sms, stream);
 }
 
 }  // namespace fa2

@@ -108,8 +108,9 @@ __device__ __forceinline__ WTile get_wtile(const FwdParams& p, int t) {
 
 // First row of key tile j that lies past the end of a packed sequence (kWN = none). Dense tensors need
 // nothing: the TMA unit fills rows past the tensor with zeros.
-__device__ __forceinline__ int wide_ragged_row(const FwdParams& p, int sk, int j) {
-  if (p.cu_q == nullptr) return kWN;
+template <bool PACKED>
+__device__ __forceinline__ int wide_ragged_row(int sk, int j) {
+  if (!PACKED) return kWN;
   const int left = sk - j * kWN;
   return left < kWN ? max(left, 0) : kWN;
 }
@@ -123,7 +124,9 @@ __device__ __forceinline__ float wide_tanh(float x) {
 // ATOMS: 64-column atoms of the head dim that are loaded (3 for head dims up to 192, else 4). TMA fills what lies
 // past the real head dim inside them with zeros, so Q K^T runs over ATOMS * 64 columns with compile-time operand
 // offsets: a runtime bound in the issuing thread's loop doubles the cost of an MMA issue.
-template <bool BF16, int ATOMS>
+// FANCY (softcap or ALiBi in use) and PACKED (cu_seqlens batches) are compile-time: the plain dense kernel carries
+// none of their code, which keeps its loops within reach of the SM's instruction cache.
+template <bool BF16, int ATOMS, bool FANCY, bool PACKED>
 __global__ void __launch_bounds__(kWThreads, 1) fwd_wide_kernel(const __grid_constant__ FwdParams p) {
   using Cfg = WideCfg;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -215,7 +218,7 @@ __global__ void __launch_bounds__(kWThreads, 1) fwd_wide_kernel(const __grid_con
     if (p.alibi != nullptr) slope = p.alibi[ti.b * p.alibi_batch_stride + ti.h] * 1.4426950408889634f;
     const float inv_cap = (p.softcap > 0.f) ? p.scale / p.softcap : 0.f;
     const float cap_l2 = p.softcap * 1.4426950408889634f;
-    const bool fancy = (p.softcap > 0.f) || (p.alibi != nullptr);
+    constexpr bool fancy = FANCY;
     bool ok = true;
     for (int i = 0; i < n_tiles; ++i) {
       const int j = ti.nb + i;
@@ -349,7 +352,7 @@ __global__ void __launch_bounds__(kWThreads, 1) fwd_wide_kernel(const __grid_con
     }
     __syncwarp();
   } else if (warp == kWLoadWarp) {
-    if (lane == 0) {
+    if (elect_one()) {
       // ---------------------------------------------------------------- loader
       uint32_t slot = 0, ring_phase = 0;
       bool ok = true;
@@ -388,7 +391,7 @@ __global__ void __launch_bounds__(kWThreads, 1) fwd_wide_kernel(const __grid_con
     // ---------------------------------------------------------------- fixer (packed batches)
     // Walks the ring in the loader's order and waits for every tile, which keeps it within one ring pass of
     // the issuer; it acts on V tiles that reach past the end of their sequence.
-    if (p.cu_q != nullptr) {
+    if (PACKED) {
       uint32_t slot = 0, ring_phase = 0;
       bool ok = true;
       auto step = [&](int first_stray) -> bool {
@@ -413,10 +416,10 @@ __global__ void __launch_bounds__(kWThreads, 1) fwd_wide_kernel(const __grid_con
       ok = step(kWN);
       for (int j = ti.nb; j < ti.ne && ok; ++j) {
         if (j + 1 < ti.ne) ok = step(kWN);
-        if (ok) ok = step(wide_ragged_row(p, ti.sk, j));
+        if (ok) ok = step(wide_ragged_row<PACKED>(ti.sk, j));
       }
     }
-  } else if (warp == kWMmaWarp && lane == 0) {
+  } else if (warp == kWMmaWarp && elect_one()) {
     // ---------------------------------------------------------------- mma issuer
     const uint32_t fmt = BF16 ? 1u : 0u;
     const uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(kWN >> 3) << 17) |
@@ -466,7 +469,7 @@ __global__ void __launch_bounds__(kWThreads, 1) fwd_wide_kernel(const __grid_con
     // O (+)= P V_i: per step of 16 keys, 32 bytes of a P row inside its atom and 16 rows of 128 bytes of V.
     auto do_v = [&](const int i) -> bool {
       if (!mbar_wait(&kv_full[slot], ring_phase, ctl, kWaitMmaKVFull)) return false;
-      if (wide_ragged_row(p, ti.sk, ti.nb + i) < kWN) {
+      if (wide_ragged_row<PACKED>(ti.sk, ti.nb + i) < kWN) {
         // A V tile that reaches past its sequence is usable once the fixer has cleared the stray rows.
         if (!mbar_wait(&kv_fixed[slot], (fix_par >> slot) & 1, ctl, kWaitMmaKVFull)) return false;
         fix_par ^= 1u << slot;
@@ -500,29 +503,41 @@ __global__ void __launch_bounds__(kWThreads, 1) fwd_wide_kernel(const __grid_con
   if (warp == kWMmaWarp) tmem_dealloc(tmem, 512);
 }
 
-template <bool BF16, int ATOMS>
+template <bool BF16, int ATOMS, bool FANCY, bool PACKED>
 cudaError_t launch_wide(const FwdParams& p, cudaStream_t stream) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(fwd_wide_kernel<BF16, ATOMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, WideCfg::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(fwd_wide_kernel<BF16, ATOMS, FANCY, PACKED>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, WideCfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
   const int64_t blocks = static_cast<int64_t>((p.seqlen_q + kWM - 1) / kWM) * p.batch * p.heads;
   if (blocks <= 0) return cudaSuccess;
   if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
-  fwd_wide_kernel<BF16, ATOMS><<<static_cast<unsigned>(blocks), kWThreads, WideCfg::kSmemBytes, stream>>>(p);
+  fwd_wide_kernel<BF16, ATOMS, FANCY, PACKED>
+      <<<static_cast<unsigned>(blocks), kWThreads, WideCfg::kSmemBytes, stream>>>(p);
   return cudaGetLastError();
+}
+
+template <bool BF16, int ATOMS>
+cudaError_t pick_features(const FwdParams& p, cudaStream_t stream) {
+  const bool fancy = (p.softcap > 0.f) || (p.alibi != nullptr);
+  const bool packed = p.cu_q != nullptr;
+  if (fancy) {
+    return packed ? launch_wide<BF16, ATOMS, true, true>(p, stream) : launch_wide<BF16, ATOMS, true, false>(p, stream);
+  }
+  return packed ? launch_wide<BF16, ATOMS, false, true>(p, stream) : launch_wide<BF16, ATOMS, false, false>(p, stream);
 }
 
 }  // namespace
 
 cudaError_t launch_fwd_wide(const FwdParams& p, int head_dim, bool bf16, cudaStream_t stream) {
   if (head_dim <= 128 || head_dim > 256 || head_dim % 8 != 0) return cudaErrorInvalidValue;
-  if (head_dim <= 192) return bf16 ? launch_wide<true, 3>(p, stream) : launch_wide<false, 3>(p, stream);
-  return bf16 ? launch_wide<true, 4>(p, stream) : launch_wide<false, 4>(p, stream);
+  if (head_dim <= 192) return bf16 ? pick_features<true, 3>(p, stream) : pick_features<false, 3>(p, stream);
+  return bf16 ? pick_features<true, 4>(p, stream) : pick_features<false, 4>(p, stream);
 }
 
 }  // namespace fa2
