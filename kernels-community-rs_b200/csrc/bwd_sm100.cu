@@ -48,7 +48,7 @@ struct BwdCfg {
   static constexpr int kDSOff = 6 * kTileBytes;    // [128 keys x 128 q] 16-bit
   static constexpr int kDSBytes = kBlk * kBlk * 2;
   static constexpr int kBarOff = kDSOff + kDSBytes;
-  static constexpr int kNumBars = 26;
+  static constexpr int kNumBars = 27;
   static constexpr int kMiscOff = (kBarOff + kNumBars * 8 + 15) / 16 * 16;  // what follows is read as float4
   static constexpr int kStatOff = kMiscOff + 32;       // lse / delta: [2 buffers][2][128] fp32
   static constexpr int kSmemBytes = kStatOff + 2 * 2 * kBlk * 4;  // the dynamic window must start 1024-aligned
@@ -166,6 +166,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   uint64_t* kv_fixed = bars + 21;  // packed batches: the fixer warp has cleared the rows past the sequence
   uint64_t* q_fixed = bars + 22;   // [2]
   uint64_t* do_fixed = bars + 24;  // [2]
+  uint64_t* dv_done = bars + 26;   // the last dV MMA has completed (dK still has one GEMM to go)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::kMiscOff + 8);
   float* s_stat = reinterpret_cast<float*>(smem + Cfg::kStatOff);
@@ -178,35 +179,28 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   if (!ti.valid) return;
   const bool want_dq = (p.which & 1) != 0;
 
-  if (tid == 0) {
-    *abort_flag = 0;
-    mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&q_full[s], 1);
-      mbar_init(&q_empty[s], 1);
+  // Descriptor fetches start first: they are the head of the latency chain of the first loads.
+  if (warp == 2 && lane == 0) {
+    tma_prefetch_desc(&p.tm_k);
+    tma_prefetch_desc(&p.tm_q);
+    tma_prefetch_desc(&p.tm_v);
+    tma_prefetch_desc(&p.tm_do);
+    tma_prefetch_desc(&p.tm_dqa);
+  }
+  if (warp == 0) {
+    // One barrier per lane: arrival counts by index (see the list above).
+    if (lane < Cfg::kNumBars) {
+      uint32_t count = 1;
+      if (lane == 10 || lane == 12 || lane == 16) count = 256;            // p_full, ds_full, stat_full
+      if (lane == 14 || lane == 18 || lane == 19 || lane == 20) count = kBlk;  // dq_free, stage_full, epi_full[2]
+      if ((lane == 7 || lane == 8) && want_dq) count = 5;  // do_empty: the dV commit and, with dQ, the four drain warps
+      mbar_init(bars + lane, count);
     }
-    for (int st = 0; st < 2; ++st) {
-      mbar_init(&do_full[st], 1);
-      mbar_init(&do_empty[st], want_dq ? 5 : 1);  // the dV commit and, with dQ, the four drain warps
-    }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 256);
-    mbar_init(dp_full, 1);
-    mbar_init(ds_full, 256);
-    mbar_init(dq_full, 1);
-    mbar_init(dq_free, 128);
-    mbar_init(dkv_done, 1);
-    mbar_init(stat_full, 256);
-    mbar_init(stage_free, 1);
-    mbar_init(stage_full, kBlk);
-    mbar_init(&epi_full[0], kBlk);
-    mbar_init(&epi_full[1], kBlk);
-    mbar_init(kv_fixed, 1);
-    for (int st = 0; st < 2; ++st) {
-      mbar_init(&q_fixed[st], 1);
-      mbar_init(&do_fixed[st], 1);
-    }
+    if (lane == 0) *abort_flag = 0;
     mbar_fence_init();
+    __syncwarp();
+  }
+  if (tid == 0) {
     // The first loads go out before the rest of the CTA is set up (TMEM allocation, the block-wide
     // barrier): their latency is the longest item of a CTA's start.
     if (ti.n_iter > 0) {
@@ -230,13 +224,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
-  }
-  if (warp == 0 && lane == 0) {
-    tma_prefetch_desc(&p.tm_q);
-    tma_prefetch_desc(&p.tm_k);
-    tma_prefetch_desc(&p.tm_v);
-    tma_prefetch_desc(&p.tm_do);
-    tma_prefetch_desc(&p.tm_dqa);
   }
   tc_fence_before();
   __syncthreads();
@@ -357,6 +344,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           });
         }
         mma_commit(&do_empty[st]);
+        if (!has_next) mma_commit(dv_done);  // dV is final: its epilogue runs beside the last dQ and dK GEMMs
         // dQ = dS K   (into the dP^T columns, which the compute warps have drained)
         ok = mbar_wait(ds_full, it & 1, ctl, kWaitBwd + 7);
         if (!ok) break;
@@ -592,7 +580,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       // with dkv_done; the Q and dO stages may still hold dQ pieces of the last iteration's drain).
       uint8_t* stage = (wg == 0) ? s_k : s_v;
       bool done = true;
-      if (n_iter > 0) done = warp_wait(dkv_done, 0, ctl, kWaitBwd + 13);
+      if (n_iter > 0) done = warp_wait(wg == 0 ? dkv_done : dv_done, 0, ctl, kWaitBwd + 13);
       if (done && store) {
         tc_fence_after();
         uint16_t* grow = gptr + ti.bq * p.dkv_batch_stride + static_cast<int64_t>(ti.k_row0 + kpos) * p.dkv_row_stride +
