@@ -345,6 +345,15 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         }
         mma_commit(&do_empty[st]);
         if (!has_next) mma_commit(dv_done);  // dV is final: its epilogue runs beside the last dQ and dK GEMMs
+        // S^T of the next iteration right behind dV, the last reader of P^T: the scores are there when the
+        // compute warps come out of phase B.
+        if (has_next) {
+          ok = q_ready(wn.mi, st ^ 1, nph, kWaitBwd + 8);
+          if (!ok) break;
+          tc_fence_after();
+          kmajor_pair(tmem + Cfg::kTmemS, k_kmaj, q_kmaj + (st ^ 1) * kTile16);
+          mma_commit(s_full);
+        }
         // dQ = dS K   (into the dP^T columns, which the compute warps have drained)
         ok = mbar_wait(ds_full, it & 1, ctl, kWaitBwd + 7);
         if (!ok) break;
@@ -355,13 +364,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
                                                                       ks.value > 0 ? 1u : 0u);
           });
           mma_commit(dq_full);
-        }
-        if (has_next) {
-          ok = q_ready(wn.mi, st ^ 1, nph, kWaitBwd + 8);
-          if (!ok) break;
-          tc_fence_after();
-          kmajor_pair(tmem + Cfg::kTmemS, k_kmaj, q_kmaj + (st ^ 1) * kTile16);
-          mma_commit(s_full);
         }
         // dK += dS^T Q
         {
