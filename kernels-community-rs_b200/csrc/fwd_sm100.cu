@@ -611,12 +611,15 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           return true;
         };
         // Ring order K(jlo), K(jlo+1), V(jlo), K(jlo+2), V(jlo+1), ...: Q K^T runs one key tile ahead of P V.
+        // (one loop from jlo - 1 instead of a peeled first step: each helper is inlined once)
         ok = load_q(0);
-        if (ti.jlo < ti.jhi && ok) ok = load_kv(&p.tm_k, ti.k_row0 + ti.jlo * kBlockN, ti.hk, ti.bq);
-        if (ok) ok = load_q(1);
-        for (int j = ti.jlo; j < ti.jhi && ok; ++j) {
+        for (int j = ti.jlo - 1; j < ti.jhi && ok; ++j) {
           if (j + 1 < ti.jhi) ok = load_kv(&p.tm_k, ti.k_row0 + (j + 1) * kBlockN, ti.hk, ti.bq);
-          if (ok) ok = load_kv(&p.tm_v, ti.k_row0 + j * kBlockN, ti.hk, ti.bq);
+          if (j < ti.jlo) {
+            if (ok) ok = load_q(1);
+          } else if (ok) {
+            ok = load_kv(&p.tm_v, ti.k_row0 + j * kBlockN, ti.hk, ti.bq);
+          }
         }
       }
       // The loader leaves last: it waits until the issuers' commits on every ring slot and on both Q stages
@@ -763,10 +766,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           advance();
           return true;
         };
-        if (ti.jlo < ti.jhi) ok = do_k(ti.jlo);
-        for (int j = ti.jlo; j < ti.jhi && ok; ++j) {
+        for (int j = ti.jlo - 1; j < ti.jhi && ok; ++j) {
           if (j + 1 < ti.jhi) ok = do_k(j + 1);
-          if (ok) ok = do_v(j);
+          if (ok && j >= ti.jlo) ok = do_v(j);
         }
         ++n_tile;
       }
