@@ -263,10 +263,22 @@ def run_ours(args, rank, world):
         launches["n"] = 0
         ms_step = timed(step, args.steps)
         launches_timed = launches["n"]
-        # Per-kernel figures for the roofline and the per-pass targets.
+        # Per-kernel figures for the roofline and the per-pass targets. Every leg starts from the same state: a
+        # pause, then its own warm-up. Without it the legs measured last come out 5-9 % slower than the same
+        # loop run first (the GPU's power management after 50-100 ms of back-to-back kernels), so the order of
+        # the legs, not the kernels, would set the figures.
+        def settle(fn):
+            barrier()
+            time.sleep(0.3)
+            for _ in range(max(3, args.warmup)):
+                fn()
+
+        settle(fwd_only)
         ms_fwd = timed(fwd_only, args.steps)
         o, lse = fwd_only()
+        settle(lambda: bwd_only(o, lse))
         ms_bwd = timed(lambda: bwd_only(o, lse), args.steps)
+        settle(lambda: bwd_only(o, lse))
         kt = []
         for _ in range(args.steps):
             bwd_only(o, lse, events=(k0, k1))
