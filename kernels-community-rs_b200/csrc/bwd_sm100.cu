@@ -48,7 +48,7 @@ struct BwdCfg {
   static constexpr int kDSOff = 6 * kTileBytes;    // [128 keys x 128 q] 16-bit
   static constexpr int kDSBytes = kBlk * kBlk * 2;
   static constexpr int kBarOff = kDSOff + kDSBytes;
-  static constexpr int kNumBars = 27;
+  static constexpr int kNumBars = 28;
   static constexpr int kMiscOff = (kBarOff + kNumBars * 8 + 15) / 16 * 16;  // what follows is read as float4
   static constexpr int kStatOff = kMiscOff + 32;       // lse / delta: [2 buffers][2][128] fp32
   static constexpr int kSmemBytes = kStatOff + 2 * 2 * kBlk * 4;  // the dynamic window must start 1024-aligned
@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   uint8_t* s_do = smem + Cfg::kDOOff;
   uint8_t* s_ds = smem + Cfg::kDSOff;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOff);
-  uint64_t* kv_full = bars + 0;
+  uint64_t* kv_full = bars + 0;    // K has landed (V has a barrier of its own: the first S^T needs only K and Q)
   uint64_t* q_full = bars + 1;    // [2]
   uint64_t* q_empty = bars + 3;   // [2]
   uint64_t* do_full = bars + 5;   // [2]
@@ -167,6 +167,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   uint64_t* q_fixed = bars + 22;   // [2]
   uint64_t* do_fixed = bars + 24;  // [2]
   uint64_t* dv_done = bars + 26;   // the last dV MMA has completed (dK still has one GEMM to go)
+  uint64_t* v_full = bars + 27;    // V has landed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::kMiscOff + 8);
   float* s_stat = reinterpret_cast<float*>(smem + Cfg::kStatOff);
@@ -206,7 +207,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     if (ti.n_iter > 0) {
       const int hq0 = ti.hk * p.group;
       const int m00 = ti.m_start * kBlk;
-      mbar_expect_tx(kv_full, 2 * Cfg::kTileBytes);
+      mbar_expect_tx(kv_full, Cfg::kTileBytes);
+      mbar_expect_tx(v_full, Cfg::kTileBytes);
       mbar_expect_tx(&q_full[0], Cfg::kTileBytes);
       mbar_expect_tx(&do_full[0], Cfg::kTileBytes);
 #pragma unroll
@@ -216,7 +218,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       }
 #pragma unroll
       for (int a = 0; a < Cfg::kAtoms; ++a) {
-        tma_load_4d(s_v + a * (kBlk * 128), &p.tm_v, kv_full, a * 64, ti.hk, ti.k_row0 + ti.n0, ti.bq);
+        tma_load_4d(s_v + a * (kBlk * 128), &p.tm_v, v_full, a * 64, ti.hk, ti.k_row0 + ti.n0, ti.bq);
         tma_load_4d(s_do + a * (kBlk * 128), &p.tm_do, &do_full[0], a * 64, hq0, ti.q_row0 + m00, ti.bq);
       }
     }
@@ -319,6 +321,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         kmajor_pair(tmem + Cfg::kTmemS, k_kmaj, q_kmaj);
         mma_commit(s_full);
         ok = do_ready(0, 0, 0, kWaitBwd + 5);
+        if (ok) ok = mbar_wait(v_full, 0, ctl, kWaitBwd + 3);
       }
       if (ok) {
         tc_fence_after();
@@ -408,7 +411,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       bool ok = true;
       const int kv_first = ti.sk - ti.n0;
       if (kv_first < kBlk) {
-        ok = __all_sync(0xffffffffu, mbar_wait(kv_full, 0, ctl, kWaitBwd + 3));
+        ok = __all_sync(0xffffffffu, mbar_wait(kv_full, 0, ctl, kWaitBwd + 3) && mbar_wait(v_full, 0, ctl, kWaitBwd + 3));
         if (ok) {
           clear_rows(s_k, kv_first);
           clear_rows(s_v, kv_first);
