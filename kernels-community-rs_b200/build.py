@@ -10,6 +10,7 @@ from __future__ import annotations
 import os
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
@@ -47,15 +48,19 @@ def build_kernels(verbose: bool = False) -> Path:
     srcs = [CSRC / s for s in KERNEL_SOURCES if (CSRC / s).exists()]
     deps = srcs + list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + [INCLUDE / "fa2_b200.h"]
     if _newer(out, deps):
-        objs = []
+        objs, jobs = [], []
         for s in srcs:
             o = LIB / (s.stem + ".o")
             if _newer(o, deps):
                 cmd = ["nvcc", *NVCC_FLAGS, "-c", str(s), "-o", str(o)]
                 if verbose:
                     cmd.insert(1, "-Xptxas=-v")
-                _run(cmd)
+                jobs.append(cmd)
             objs.append(str(o))
+        # one nvcc per translation unit, side by side: every kernel file holds 16 instantiations
+        if jobs:
+            with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 1)) as pool:
+                list(pool.map(_run, jobs))
         _run(["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(out), *objs,
               "-Xcompiler", "-fPIC"])
     return out
