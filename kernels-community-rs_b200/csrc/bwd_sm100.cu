@@ -35,6 +35,9 @@ constexpr int kThreads = 512;
 constexpr int kComputeRegs = 152;
 constexpr int kDrainRegs = 152;
 constexpr int kMiscRegs = 56;
+// setmaxnreg moves registers inside the CTA's own allocation (128 per thread at launch: 65536 / 512). What the
+// compute and drain warps take must not exceed what warps 0-3 give back: an increase beyond it never returns.
+static_assert(8 * (kComputeRegs - 128) + 4 * (kDrainRegs - 128) <= 4 * (128 - kMiscRegs), "setmaxnreg: more registers asked for than released");
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int D>

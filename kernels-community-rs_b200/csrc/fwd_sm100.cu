@@ -60,6 +60,10 @@ constexpr int kLoadWarp = 9;
 constexpr int kFixWarp = 11;
 constexpr int kSoftmaxRegs = 200;
 constexpr int kOtherRegs = 104;
+// setmaxnreg moves registers inside the CTA's own allocation (168 per thread at launch: 65536 / 384 rounded down
+// to a multiple of 8). What the softmax warps take must not exceed what the other warps give back: an increase
+// beyond it never returns (a build with 208 / 96 hung the kernel), and no bounded wait can cover that instruction.
+static_assert(8 * (kSoftmaxRegs - 168) <= 4 * (168 - kOtherRegs), "setmaxnreg: the softmax warps ask for more than the others release");
 constexpr int kPQ = FA2_PQ;                        // P is handed to the MMA warp in kPQ pieces of kBlockN / kPQ keys
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain
 
