@@ -182,6 +182,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   const KvTile ti = get_kv_tile(p, blockIdx.x);
   if (!ti.valid) return;
   const bool want_dq = (p.which & 1) != 0;
+  const bool want_dkv = (p.which & 2) != 0;  // a dQ-only call skips the dV and dK GEMMs (their commits still hand the stages back)
 
   // Descriptor fetches start first: they are the head of the latency chain of the first loads.
   if (warp == 2 && lane == 0) {
@@ -342,7 +343,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         ok = mbar_wait(p_full, it & 1, ctl, kWaitBwd + 6);
         if (!ok) break;
         tc_fence_after();
-        {
+        if (want_dkv) {
           const uint64_t b = do_mn + st * kTile16;
           static_for<kBlk / 16>([&](auto ks) {
             mma_ts_o<(ks.value / 4) * 64 + (ks.value % 4) * 8, ks.value * (2048 >> 4)>(
@@ -372,7 +373,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           mma_commit(dq_full);
         }
         // dK += dS^T Q
-        {
+        if (want_dkv) {
           const uint64_t b = q_mn + st * kTile16;
           static_for<kBlk / 16>([&](auto ks) {
             mma_ss_o<(ks.value / 4) * kAtom16 + (ks.value % 4) * 2, ks.value * (2048 >> 4)>(
