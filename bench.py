@@ -259,32 +259,34 @@ def run_ours(args, rank, world):
 
     for _ in range(args.warmup):
         step()
+    # The clock record covers the timed region of `value` only: the legs below pause between kernels, and an
+    # idle GPU's clock says nothing about the run.
     with ClockSampler(local) as clocks:
         launches["n"] = 0
         ms_step = timed(step, args.steps)
         launches_timed = launches["n"]
-        # Per-kernel figures for the roofline and the per-pass targets. Every leg starts from the same state: a
-        # pause, then its own warm-up. Without it the legs measured last come out 5-9 % slower than the same
-        # loop run first (the GPU's power management after 50-100 ms of back-to-back kernels), so the order of
-        # the legs, not the kernels, would set the figures.
-        def settle(fn):
-            barrier()
-            time.sleep(0.3)
-            for _ in range(max(3, args.warmup)):
-                fn()
+    # Per-kernel figures for the roofline and the per-pass targets. Every leg starts from the same state: a
+    # pause, then its own warm-up. Without it the legs measured last come out 5-9 % slower than the same
+    # loop run first (the GPU's power management after 50-100 ms of back-to-back kernels), so the order of
+    # the legs, not the kernels, would set the figures.
+    def settle(fn):
+        barrier()
+        time.sleep(0.3)
+        for _ in range(max(3, args.warmup)):
+            fn()
 
-        settle(fwd_only)
-        ms_fwd = timed(fwd_only, args.steps)
-        o, lse = fwd_only()
-        settle(lambda: bwd_only(o, lse))
-        ms_bwd = timed(lambda: bwd_only(o, lse), args.steps)
-        settle(lambda: bwd_only(o, lse))
-        kt = []
-        for _ in range(args.steps):
-            bwd_only(o, lse, events=(k0, k1))
-            torch.cuda.synchronize()
-            kt.append(k0.elapsed_time(k1))
-        ms_bwd_kernel = sum(kt) / len(kt)
+    settle(fwd_only)
+    ms_fwd = timed(fwd_only, args.steps)
+    o, lse = fwd_only()
+    settle(lambda: bwd_only(o, lse))
+    ms_bwd = timed(lambda: bwd_only(o, lse), args.steps)
+    settle(lambda: bwd_only(o, lse))
+    kt = []
+    for _ in range(args.steps):
+        bwd_only(o, lse, events=(k0, k1))
+        torch.cuda.synchronize()
+        kt.append(k0.elapsed_time(k1))
+    ms_bwd_kernel = sum(kt) / len(kt)
     status = ops.device_status()
     if status != 0:
         raise RuntimeError(f"kernel pipeline reported a stalled wait (status {status})")
